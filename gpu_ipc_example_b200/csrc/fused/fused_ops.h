@@ -1,0 +1,28 @@
+// Host entry points of the fused collectives (all-reduce + residual-add + RMSNorm,
+// all-reduce + scale/cast, row-parallel GEMM + all-reduce).  No counterpart in the
+// reference; they serve the tensor-parallel inference use it was written for
+// (script/gpu_inference_test.py:29-45 all-reduces decode-sized activations).
+#pragma once
+
+#include "../coll/comm.h"
+
+namespace b200ipc {
+
+struct FusedNormPtrs {
+  const void* x;         // [rows, hidden] partial activations of this rank
+  const void* residual;  // [rows, hidden]
+  const void* gamma;     // [hidden]
+  void* out;             // [rows, hidden] normalised
+  void* residual_out;    // [rows, hidden] sum + residual (may alias residual)
+};
+
+// out = RMSNorm(all_reduce(x) + residual) * gamma ; residual_out = all_reduce(x) + residual.
+// One kernel, one NVLink hop.  hidden must be a multiple of 8.  ptrs holds nlocal() entries.
+CollInfo fused_allreduce_residual_rmsnorm(Comm& comm, DType t, const FusedNormPtrs* ptrs, int64_t rows, int64_t hidden,
+                                          float eps, int ctas, cudaStream_t stream);
+
+// out = cast<tout>(all_reduce(in) * scale).
+CollInfo fused_allreduce_scale_cast(Comm& comm, DType tin, DType tout, const void* const* ins, void* const* outs,
+                                    size_t nelems, float scale, int ctas, cudaStream_t stream);
+
+}  // namespace b200ipc

@@ -1,0 +1,211 @@
+// One-shot all-reduce fused with what follows it in a tensor-parallel layer:
+//   kEpiNorm   y = RMSNorm(sum_over_ranks(x) + residual) * gamma, and the pre-norm
+//              sum is written back as the new residual;
+//   kEpiScale  y = cast<Tout>(sum_over_ranks(x) * scale).
+// Every rank pushes its partial activations to all peers as LL512 transactions
+// (480 B payload per 512 B store, a flag closing each 64 B), adds the world copies
+// in rank order in fp32 registers and applies the epilogue before anything is
+// written to HBM: one NVLink hop, one read of x/residual, one write of the outputs.
+// A CTA owns whole rows, so the row statistic never leaves the SM.
+//
+// No counterpart in the reference (its collectives are not fused with compute);
+// the wire format and the one-shot schedule are the ones of proto/ and coll/.
+#pragma once
+
+#include "../coll/schedules.h"
+#include "../proto/dev_backend.cuh"
+
+namespace b200ipc {
+
+constexpr int kEpiNorm = 0;
+constexpr int kEpiScale = 1;
+constexpr int kFusedMaxRowsPerCta = 64;
+
+template <typename Tout>
+__device__ __forceinline__ uint32_t pack_out(float a, float b) { return Cvt<Tout>::down(a, b); }
+
+template <typename T, typename Tout, int N, int EPI>
+__global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_constant__ KArgs args) {
+  using B = DevBackend<ProtoKind::LL512, T>;
+  const RankView& me = args.v[blockIdx.y];
+  const int r = me.rank;
+  const int lane = int(threadIdx.x & 31);
+  const int warp = int(threadIdx.x >> 5);
+  const int warps = int(blockDim.x >> 5);
+  const int wire = int(blockIdx.x) * warps + warp;
+
+  uint32_t seq = me.seq;
+  if (me.seq_dev) seq += ld_volatile_u32(me.seq_dev);
+
+  DevWaiter waiter;
+  waiter.me = &me;
+  waiter.ctrl_off = args.lay.ctrl_off;
+  waiter.wire = wire;
+
+  const uint32_t* in = static_cast<const uint32_t*>(me.in);
+  const int64_t total_dw = int64_t(me.nelems / 2);
+
+  // This CTA's range of dwords [d0, d1).
+  int64_t d0, d1;
+  int row0 = 0, nrows = 0;
+  int64_t row_dw = 0;
+  if (EPI == kEpiNorm) {
+    const int hidden = int(uint32_t(me.aux[3]));
+    row_dw = hidden / 2;
+    const int rows = int(total_dw / row_dw);
+    const int per = (rows + int(gridDim.x) - 1) / int(gridDim.x);
+    row0 = int(blockIdx.x) * per;
+    int row1 = row0 + per;
+    if (row1 > rows) row1 = rows;
+    nrows = row1 > row0 ? row1 - row0 : 0;
+    d0 = int64_t(row0) * row_dw;
+    d1 = d0 + int64_t(nrows) * row_dw;
+  } else {
+    int64_t per = ceil_div64(total_dw, int64_t(gridDim.x));
+    per = round_up64(per, 4);
+    d0 = int64_t(blockIdx.x) * per;
+    d1 = min64(d0 + per, total_dw);
+    if (d1 < d0) d1 = d0;
+  }
+  const int64_t ntx = ceil_div64(d1 - d0, B::kPayloadDw);
+
+  __shared__ float s_sumsq[kFusedMaxRowsPerCta];
+  __shared__ int s_abort;
+  if (threadIdx.x < kFusedMaxRowsPerCta) s_sumsq[threadIdx.x] = 0.f;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+
+  const uint32_t* residual = reinterpret_cast<const uint32_t*>(me.aux[0]);
+  uint32_t* res_out = reinterpret_cast<uint32_t*>(me.aux[2]);
+  uint32_t* out = static_cast<uint32_t*>(me.out);
+  const float scale = __uint_as_float(uint32_t(me.aux[3] >> 32));  // kEpiScale: multiplier; kEpiNorm: eps
+
+  bool ok = true;
+  for (int64_t k = 0; ok; ++k) {
+    const int64_t j = warp + k * warps;
+    if (j >= ntx) break;
+    const uint32_t flag = seq + uint32_t(k);
+    const int slot = int(flag % kOneShotSlots);
+    const int64_t dw = d0 + j * B::kPayloadDw;
+    auto at = [&](char* heap, int src) {
+      return heap + args.lay.oneshot_off +
+             ((int64_t(src) * kMaxOneShotWires + wire) * kOneShotSlots + slot) * kOneShotStride;
+    };
+    typename B::Msg v;
+    B::load(v, in, dw, d1, -1);
+    B::shuffle(v);
+    if (N > 1) {
+      B::set_flags(v, flag);
+      if (!(me.flags & kMuteSends)) {
+#pragma unroll
+        for (int i = 1; i < N; ++i) {
+          const int q = (r + i) % N;
+          B::send(at(me.peer[q], r), v);
+        }
+      }
+    }
+    typename B::Acc a;
+    typename B::Msg m;
+    if (r == 0) {
+      B::acc_init(a, v);
+    } else {
+      ok = B::wait(waiter, m, at(me.heap, 0), flag, 5, 0, k, r);
+      if (!ok) break;
+      B::acc_init(a, m);
+    }
+#pragma unroll
+    for (int q = 1; q < N; ++q) {
+      if (q == r) {
+        B::acc_add(a, v, false);
+      } else {
+        ok = B::wait(waiter, m, at(me.heap, q), flag, 5, q, k, r);
+        if (!ok) break;
+        B::acc_add(a, m, false);
+      }
+    }
+    if (!ok) break;
+
+    if (EPI == kEpiNorm) {
+      typename B::Msg rv;
+      B::load(rv, residual, dw, d1, -1);
+      B::shuffle(rv);
+      B::acc_add(a, rv, false);
+      B::acc_to_msg(v, a);
+      B::restore(v);
+      B::store(res_out, dw, d1, -1, v);
+      // sum of squares of the rounded values, per row
+      float ss = 0.f;
+      const int64_t first_row = dw / row_dw;
+      const int64_t last_dw = min64(dw + B::kPayloadDw, d1) - 1;
+      const bool one_row = (last_dw / row_dw) == first_row;
+      if (lane < 30) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t idx = dw + 4 * lane + e;
+          if (idx < d1) {
+            float2 x = Cvt<T>::up(v.d[e]);
+            const float s = x.x * x.x + x.y * x.y;
+            if (one_row) ss += s;
+            else atomicAdd(&s_sumsq[int(idx / row_dw) - row0], s);
+          }
+        }
+      }
+      if (one_row) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) atomicAdd(&s_sumsq[int(first_row) - row0], ss);
+      }
+    } else {
+      // scale and cast; lanes 30/31 carry displaced dwords, so restore first
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a.f[e] *= scale;
+      typename B::Msg o;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o.d[e] = pack_out<Tout>(a.f[2 * e], a.f[2 * e + 1]);
+      B::restore(o);
+      B::store(out, dw, d1, -1, o);
+    }
+  }
+  if (!ok) s_abort = 1;
+  __syncthreads();
+
+  if (EPI == kEpiNorm && s_abort == 0) {
+    const int hidden = int(uint32_t(me.aux[3]));
+    const float eps = scale;
+    const uint4* gamma = reinterpret_cast<const uint4*>(me.aux[1]);
+    const int row_vec = hidden / 8;
+    for (int rr = 0; rr < nrows; ++rr) {
+      const float inv = rsqrtf(s_sumsq[rr] / float(hidden) + eps);
+      const uint4* src = reinterpret_cast<const uint4*>(res_out + (int64_t(row0 + rr)) * row_dw);
+      uint4* dst = reinterpret_cast<uint4*>(out + (int64_t(row0 + rr)) * row_dw);
+      for (int i = int(threadIdx.x); i < row_vec; i += int(blockDim.x)) {
+        const uint4 x = src[i];
+        const uint4 g = gamma[i];
+        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+        const uint32_t gs[4] = {g.x, g.y, g.z, g.w};
+        uint32_t ys[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = Cvt<T>::up(xs[e]);
+          const float2 gf = Cvt<T>::up(gs[e]);
+          ys[e] = Cvt<T>::down(xf.x * inv * gf.x, xf.y * inv * gf.y);
+        }
+        dst[i] = make_uint4(ys[0], ys[1], ys[2], ys[3]);
+      }
+    }
+  }
+
+  if (me.seq_dev) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(me.seq_dev + 1, 1u) == gridDim.x - 1) {
+        me.seq_dev[1] = 0;
+        me.seq_dev[0] += me.seq_step;
+        __threadfence();
+      }
+    }
+  }
+}
+
+}  // namespace b200ipc

@@ -1,0 +1,318 @@
+// PyTorch binding: custom ops in the `b200ipc` namespace that run the
+// collectives on the current CUDA stream of the tensors' device, plus plain
+// pybind functions for communicator life-cycle and introspection.
+//
+// Capability parity: the reference's framework smoke test drives an all-reduce
+// of fp16 activations through a torch process group (script/gpu_inference_test.py:
+// 21-45); here the same call lands in this library's kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+#include <torch/library.h>
+
+#include <map>
+#include <memory>
+#include <mutex>
+
+#include "../bootstrap/unix_mesh.h"
+#include "../coll/comm.h"
+#include "../common/check.h"
+#include "../fused/fused_ops.h"
+
+namespace {
+
+using namespace b200ipc;
+
+struct Entry {
+  std::unique_ptr<UnixMesh> mesh;
+  std::unique_ptr<Comm> comm;
+};
+
+std::mutex g_mu;
+std::map<int64_t, Entry> g_comms;
+int64_t g_next_id = 1;
+
+Comm& get(int64_t id) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_comms.find(id);
+  TORCH_CHECK(it != g_comms.end(), "b200ipc: unknown communicator id ", id);
+  return *it->second.comm;
+}
+
+HeapBacking parse_backing(const std::string& s) {
+  if (s == "auto") return HeapBacking::Auto;
+  if (s == "vmm-fd" || s == "vmm") return HeapBacking::VmmFd;
+  if (s == "cuda-ipc" || s == "ipc") return HeapBacking::CudaIpc;
+  if (s == "host-shm" || s == "host") return HeapBacking::HostShm;
+  TORCH_CHECK(false, "b200ipc: unknown backing '", s, "'");
+}
+
+CommOptions make_options(int64_t staging_bytes, bool nvls, int64_t timeout_ms, const std::string& backing,
+                         bool device_seq, int64_t first_seq, int64_t max_ctas) {
+  CommOptions o;
+  o.heap.staging_bytes = size_t(staging_bytes);
+  o.heap.nvls = nvls;
+  o.heap.backing = parse_backing(backing);
+  o.timeout_ms = uint64_t(timeout_ms);
+  o.device_seq = device_seq;
+  o.first_seq = uint32_t(first_seq);
+  o.max_ctas = int(max_ctas);
+  return o;
+}
+
+int64_t comm_create(int64_t rank, int64_t world, int64_t device, const std::string& job_id, int64_t instance,
+                    int64_t staging_bytes, bool nvls, int64_t timeout_ms, const std::string& backing, bool device_seq,
+                    int64_t first_seq, int64_t max_ctas, int64_t bootstrap_timeout_ms) {
+  Entry e;
+  MeshOptions mo;
+  mo.job_id = job_id;
+  mo.instance = int(instance);
+  mo.timeout_ms = int(bootstrap_timeout_ms);
+  e.mesh = std::make_unique<UnixMesh>(int(rank), int(world), mo);
+  e.comm = Comm::create(*e.mesh, int(device),
+                        make_options(staging_bytes, nvls, timeout_ms, backing, device_seq, first_seq, max_ctas));
+  std::lock_guard<std::mutex> lk(g_mu);
+  int64_t id = g_next_id++;
+  g_comms[id] = std::move(e);
+  return id;
+}
+
+int64_t comm_create_virtual(int64_t world, int64_t device, int64_t staging_bytes, int64_t timeout_ms, bool device_seq,
+                            int64_t first_seq, int64_t max_ctas) {
+  Entry e;
+  e.comm = Comm::create_virtual(int(world), int(device),
+                                make_options(staging_bytes, false, timeout_ms, "auto", device_seq, first_seq, max_ctas));
+  std::lock_guard<std::mutex> lk(g_mu);
+  int64_t id = g_next_id++;
+  g_comms[id] = std::move(e);
+  return id;
+}
+
+void comm_destroy(int64_t id) {
+  Entry e;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_comms.find(id);
+    if (it == g_comms.end()) return;
+    e = std::move(it->second);
+    g_comms.erase(it);
+  }
+  e.comm->finalize();
+  e.comm.reset();
+  e.mesh.reset();
+}
+
+DType dtype_of(const at::Tensor& t) {
+  if (t.scalar_type() == at::kHalf) return DType::F16;
+  if (t.scalar_type() == at::kBFloat16) return DType::BF16;
+  TORCH_CHECK(false, "b200ipc: only float16 and bfloat16 tensors are supported, got ", t.scalar_type());
+}
+
+void check_tensors(Comm& c, const std::vector<at::Tensor>& ts, const char* what) {
+  TORCH_CHECK(int(ts.size()) == c.nlocal(), "b200ipc: expected ", c.nlocal(), " ", what, " tensor(s), got ", ts.size());
+  for (const auto& t : ts) {
+    TORCH_CHECK(t.is_cuda() && t.get_device() == c.device(), "b200ipc: ", what, " must live on cuda:", c.device());
+    TORCH_CHECK(t.is_contiguous(), "b200ipc: ", what, " must be contiguous");
+  }
+}
+
+AlgoSpec algo_or_throw(const std::string& name, bool want_allgather) {
+  AlgoSpec a;
+  bool ag = false;
+  TORCH_CHECK(parse_algo(name, &a, &ag), "b200ipc: unknown algorithm '", name, "'. Known: ", algo_names_help());
+  if (a.automatic) return a;
+  TORCH_CHECK(ag == want_allgather || a.sched == SchedKind::Bulk || a.sched == SchedKind::Nvls,
+              "b200ipc: algorithm '", name, "' is for ", ag ? "all-gather" : "all-reduce");
+  return a;
+}
+
+std::vector<int64_t> info_vec(const CollInfo& i) {
+  return {int64_t(i.sched), int64_t(i.proto), i.ctas, i.warps, i.nwires, i.steps, int64_t(i.first_flag), i.launches,
+          int64_t(i.staged)};
+}
+
+std::vector<int64_t> all_reduce(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int64_t comm_id,
+                                const std::string& algo, int64_t ctas, int64_t warps, int64_t flags) {
+  Comm& c = get(comm_id);
+  check_tensors(c, ins, "input");
+  check_tensors(c, outs, "output");
+  std::vector<const void*> ip;
+  std::vector<void*> op;
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(ins[i].numel() == ins[0].numel() && outs[i].numel() == ins[0].numel(), "b200ipc: size mismatch");
+    TORCH_CHECK(ins[i].scalar_type() == outs[i].scalar_type(), "b200ipc: dtype mismatch");
+    ip.push_back(ins[i].data_ptr());
+    op.push_back(outs[i].data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  LaunchGeom g{int(ctas), int(warps)};
+  CollInfo info = c.all_reduce(algo_or_throw(algo, false), dtype_of(ins[0]), ip.data(), op.data(), size_t(ins[0].numel()), g,
+                               at::cuda::getCurrentCUDAStream(c.device()), uint32_t(flags));
+  return info_vec(info);
+}
+
+std::vector<int64_t> all_gather(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int64_t comm_id,
+                                const std::string& algo, int64_t ctas, int64_t warps, int64_t flags) {
+  Comm& c = get(comm_id);
+  check_tensors(c, ins, "input");
+  check_tensors(c, outs, "output");
+  std::vector<const void*> ip;
+  std::vector<void*> op;
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(outs[i].numel() == ins[i].numel() * c.world(), "b200ipc: output must hold world * input elements");
+    ip.push_back(ins[i].data_ptr());
+    op.push_back(outs[i].data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  LaunchGeom g{int(ctas), int(warps)};
+  CollInfo info = c.all_gather(algo_or_throw(algo, true), dtype_of(ins[0]), ip.data(), op.data(), size_t(ins[0].numel()), g,
+                               at::cuda::getCurrentCUDAStream(c.device()), uint32_t(flags));
+  return info_vec(info);
+}
+
+std::vector<int64_t> reduce_scatter(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int64_t comm_id,
+                                    const std::string& algo, int64_t ctas, int64_t flags) {
+  Comm& c = get(comm_id);
+  check_tensors(c, ins, "input");
+  check_tensors(c, outs, "output");
+  std::vector<const void*> ip;
+  std::vector<void*> op;
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(ins[i].numel() == outs[i].numel() * c.world(), "b200ipc: input must hold world * output elements");
+    ip.push_back(ins[i].data_ptr());
+    op.push_back(outs[i].data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  LaunchGeom g{int(ctas), 0};
+  AlgoSpec a = algo_or_throw(algo, false);
+  CollInfo info = c.reduce_scatter(a, dtype_of(ins[0]), ip.data(), op.data(), size_t(ins[0].numel()), g,
+                                   at::cuda::getCurrentCUDAStream(c.device()), uint32_t(flags));
+  return info_vec(info);
+}
+
+// In-place single-tensor form, the shape `dist.all_reduce(t)` has.
+at::Tensor all_reduce_(at::Tensor t, int64_t comm_id, const std::string& algo) {
+  all_reduce({t}, {t}, comm_id, algo, 0, 0, 0);
+  return t;
+}
+
+at::Tensor sym_empty(int64_t comm_id, std::vector<int64_t> shape, at::ScalarType dtype, int64_t local) {
+  Comm& c = get(comm_id);
+  int64_t n = 1;
+  for (int64_t s : shape) n *= s;
+  size_t bytes = size_t(n) * c10::elementSize(dtype);
+  size_t off;
+  if (local == 0) {
+    off = c.sym_alloc(bytes);
+    // remember for the other local ranks of a virtual world
+    c.set_last_sym_offset(off);
+  } else {
+    off = c.last_sym_offset();
+  }
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, c.device());
+  return at::from_blob(c.sym_ptr(off, int(local)), shape, opts);
+}
+
+std::vector<int64_t> fused_ar_rmsnorm(std::vector<at::Tensor> ins, std::vector<at::Tensor> residuals,
+                                      std::vector<at::Tensor> gammas, std::vector<at::Tensor> outs,
+                                      std::vector<at::Tensor> res_outs, double eps, int64_t comm_id, int64_t ctas) {
+  Comm& c = get(comm_id);
+  check_tensors(c, ins, "input");
+  check_tensors(c, outs, "output");
+  check_tensors(c, residuals, "residual");
+  check_tensors(c, gammas, "gamma");
+  check_tensors(c, res_outs, "residual output");
+  TORCH_CHECK(ins[0].dim() == 2, "b200ipc: fused all-reduce + RMSNorm takes [rows, hidden] tensors");
+  const int64_t rows = ins[0].size(0), hidden = ins[0].size(1);
+  std::vector<FusedNormPtrs> p(size_t(c.nlocal()));
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(ins[i].sizes() == ins[0].sizes() && outs[i].sizes() == ins[0].sizes() &&
+                    residuals[i].sizes() == ins[0].sizes() && res_outs[i].sizes() == ins[0].sizes() &&
+                    gammas[i].numel() == hidden,
+                "b200ipc: shape mismatch");
+    p[size_t(i)] = {ins[i].data_ptr(), residuals[i].data_ptr(), gammas[i].data_ptr(), outs[i].data_ptr(),
+                    res_outs[i].data_ptr()};
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  CollInfo info = fused_allreduce_residual_rmsnorm(c, dtype_of(ins[0]), p.data(), rows, hidden, float(eps), int(ctas),
+                                                   at::cuda::getCurrentCUDAStream(c.device()));
+  return info_vec(info);
+}
+
+std::vector<int64_t> fused_ar_scale_cast(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, double scale,
+                                         int64_t comm_id, int64_t ctas) {
+  Comm& c = get(comm_id);
+  check_tensors(c, ins, "input");
+  check_tensors(c, outs, "output");
+  std::vector<const void*> ip;
+  std::vector<void*> op;
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(ins[i].numel() == outs[i].numel(), "b200ipc: size mismatch");
+    ip.push_back(ins[i].data_ptr());
+    op.push_back(outs[i].data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  CollInfo info = fused_allreduce_scale_cast(c, dtype_of(ins[0]), dtype_of(outs[0]), ip.data(), op.data(),
+                                             size_t(ins[0].numel()), float(scale), int(ctas),
+                                             at::cuda::getCurrentCUDAStream(c.device()));
+  return info_vec(info);
+}
+
+}  // namespace
+
+TORCH_LIBRARY(b200ipc, m) {
+  m.def("all_reduce(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_reduce);
+  m.def("all_gather(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_gather);
+  m.def("reduce_scatter(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int flags) -> int[]", &reduce_scatter);
+  m.def("all_reduce_(Tensor(a!) t, int comm, str algo) -> Tensor(a!)", &all_reduce_);
+  m.def(
+      "fused_ar_rmsnorm(Tensor[] ins, Tensor[] residuals, Tensor[] gammas, Tensor[] outs, Tensor[] res_outs, float eps, "
+      "int comm, int ctas) -> int[]",
+      &fused_ar_rmsnorm);
+  m.def("fused_ar_scale_cast(Tensor[] ins, Tensor[] outs, float scale, int comm, int ctas) -> int[]", &fused_ar_scale_cast);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "b200ipc native extension";
+  m.def("comm_create", &comm_create);
+  m.def("comm_create_virtual", &comm_create_virtual);
+  m.def("comm_destroy", &comm_destroy);
+  m.def("sym_empty", &sym_empty);
+  m.def("sym_free_all", [](int64_t id) { get(id).sym_free_all(); });
+  m.def("world", [](int64_t id) { return get(id).world(); });
+  m.def("nlocal", [](int64_t id) { return get(id).nlocal(); });
+  m.def("rank", [](int64_t id, int64_t local) { return get(id).rank(int(local)); });
+  m.def("has_nvls", [](int64_t id) { return get(id).has_nvls(); });
+  m.def("nvls_note", [](int64_t id) { return get(id).heap(0).nvls_note(); });
+  m.def("backing", [](int64_t id) { return std::string(backing_name(get(id).heap(0).backing())); });
+  m.def("launches", [](int64_t id) { return get(id).launches(); });
+  m.def("seq", [](int64_t id) { return int64_t(get(id).seq()); });
+  m.def("set_seq", [](int64_t id, int64_t s) { get(id).set_seq(uint32_t(s)); });
+  m.def("set_timeout_ms", [](int64_t id, int64_t ms) { get(id).set_timeout_ms(uint64_t(ms)); });
+  m.def("set_thresholds", [](int64_t id, int64_t a, int64_t b) { get(id).set_thresholds(size_t(a), size_t(b)); });
+  m.def("host_barrier", [](int64_t id) { get(id).host_barrier(); });
+  m.def("reset", [](int64_t id) { get(id).reset(); });
+  m.def("raise_if_failed", [](int64_t id) { get(id).raise_if_failed(); });
+  m.def("status", [](int64_t id, int64_t local) {
+    StatusBlock s = get(id).status(int(local));
+    return std::vector<int64_t>{s.code, s.rank, s.peer, s.wire, s.step, s.expected, s.seen, s.where};
+  });
+  m.def("dump_heap", [](int64_t id, int64_t local, int64_t offset, int64_t bytes) {
+    at::Tensor t = at::empty({bytes}, at::TensorOptions().dtype(at::kByte));
+    get(id).heap(int(local)).dump(size_t(offset), size_t(bytes), t.data_ptr());
+    return t;
+  });
+  m.def("heap_layout", [](int64_t id) {
+    const HeapLayout& l = get(id).heap(0).layout();
+    return std::vector<int64_t>{int64_t(l.ctrl_off),     int64_t(l.half_off[0]),  int64_t(l.half_off[1]),
+                                int64_t(l.half_bytes),   int64_t(l.oneshot_off),  int64_t(l.oneshot_bytes),
+                                int64_t(l.staging_off),  int64_t(l.staging_bytes), int64_t(l.total_bytes)};
+  });
+  m.def("algo_names", &algo_names_help);
+  m.def("socket_name", [](const std::string& job, int64_t instance, int64_t rank) {
+    MeshOptions mo;
+    mo.job_id = job;
+    mo.instance = int(instance);
+    return UnixMesh::socket_name(mo, int(rank));
+  });
+}

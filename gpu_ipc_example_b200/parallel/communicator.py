@@ -1,0 +1,276 @@
+"""Python face of the communicator.
+
+One `Communicator` drives either this process's rank of a multi-process world
+(one process per GPU, `torchrun`/`mpirun`/own launcher) or, with
+`Communicator.virtual(n)`, all `n` ranks of a world emulated on a single GPU.
+In the second form every tensor argument is a list with one tensor per rank.
+
+The intended consumer is the one the reference's smoke script shows
+(script/gpu_inference_test.py:21-45): `all_reduce` of fp16 activations inside
+tensor-parallel inference.
+"""
+from __future__ import annotations
+
+import os
+import uuid
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .._ext import load
+
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+SCHED_NAMES = ["parallel", "sequential", "ring", "bisect", "oneshot", "bulk", "nvls"]
+PROTO_NAMES = ["LL8", "LL16", "LL128", "LL512"]
+
+FLAG_ROUND_EACH_ADD = 1  # sum in the element type like the reference (rt64_128.hpp:950-966)
+FLAG_MUTE_SENDS = 2      # fault injection: this rank sends nothing
+
+
+@dataclass
+class CollInfo:
+    sched: str
+    proto: str
+    ctas: int
+    warps: int
+    nwires: int
+    steps: int
+    first_flag: int
+    launches: int
+    staged: bool
+
+    @classmethod
+    def from_vec(cls, v):
+        return cls(SCHED_NAMES[v[0]], PROTO_NAMES[v[1]], v[2], v[3], v[4], v[5], v[6], v[7], bool(v[8]))
+
+
+class CollectiveError(RuntimeError):
+    """A device-side bounded wait ran out or a peer aborted."""
+
+
+def _env_rank():
+    for r, w, l in (("B200IPC_RANK", "B200IPC_WORLD", "B200IPC_LOCAL_RANK"), ("RANK", "WORLD_SIZE", "LOCAL_RANK"),
+                    ("OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_RANK"),
+                    ("PMI_RANK", "PMI_SIZE", "MPI_LOCALRANKID"), ("SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID")):
+        if r in os.environ and w in os.environ:
+            rank, world = int(os.environ[r]), int(os.environ[w])
+            return rank, world, int(os.environ.get(l, rank))
+    return 0, 1, 0
+
+
+class Communicator:
+    def __init__(self, handle: int, virtual: bool):
+        self._C = load()
+        self._h = handle
+        self._virtual = virtual
+        self.world = self._C.world(handle)
+        self.nlocal = self._C.nlocal(handle)
+        self.rank = self._C.rank(handle, 0)
+        self.last_info: Optional[CollInfo] = None
+
+    # ------------------------------------------------------------------ creation
+    @classmethod
+    def create(cls, rank: Optional[int] = None, world: Optional[int] = None, device: Optional[int] = None, *,
+               job_id: Optional[str] = None, instance: int = 0, staging_bytes: int = 256 << 20, nvls: bool = False,
+               timeout_ms: int = 2000, backing: str = "auto", device_seq: bool = False, first_seq: int = 1,
+               max_ctas: int = 0, bootstrap_timeout_ms: int = 60000) -> "Communicator":
+        """Collective: every rank of the job calls it.  Rank, world size and the
+        device default to what the launcher put into the environment."""
+        C = load()
+        erank, eworld, elocal = _env_rank()
+        rank = erank if rank is None else rank
+        world = eworld if world is None else world
+        device = elocal if device is None else device
+        if job_id is None:
+            job_id = os.environ.get("B200IPC_JOB_ID") or ("port" + os.environ["MASTER_PORT"] if "MASTER_PORT" in os.environ else "default")
+        h = C.comm_create(rank, world, device, job_id, instance, staging_bytes, nvls, timeout_ms, backing, device_seq,
+                          first_seq, max_ctas, bootstrap_timeout_ms)
+        return cls(h, False)
+
+    @classmethod
+    def from_torch_distributed(cls, device: Optional[int] = None, **kw) -> "Communicator":
+        """Uses an initialised `torch.distributed` group for rank/world and to agree on a job id."""
+        import torch.distributed as dist
+
+        rank, world = dist.get_rank(), dist.get_world_size()
+        token = [uuid.uuid4().hex if rank == 0 else None]
+        dist.broadcast_object_list(token, src=0)
+        if device is None:
+            device = int(os.environ.get("LOCAL_RANK", rank))
+        return cls.create(rank, world, device, job_id=token[0], **kw)
+
+    @classmethod
+    def virtual(cls, world: int, device: int = 0, *, staging_bytes: int = 64 << 20, timeout_ms: int = 2000,
+                device_seq: bool = False, first_seq: int = 1, max_ctas: int = 0) -> "Communicator":
+        """All `world` ranks emulated on one GPU (one cooperative launch per collective)."""
+        C = load()
+        h = C.comm_create_virtual(world, device, staging_bytes, timeout_ms, device_seq, first_seq, max_ctas)
+        return cls(h, True)
+
+    def close(self):
+        if self._h is not None:
+            self._C.comm_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # ------------------------------------------------------------------ helpers
+    def _lists(self, x: TensorOrList) -> List[torch.Tensor]:
+        if isinstance(x, torch.Tensor):
+            if self.nlocal != 1:
+                raise ValueError(f"this communicator drives {self.nlocal} ranks: pass one tensor per rank")
+            return [x]
+        x = list(x)
+        if len(x) != self.nlocal:
+            raise ValueError(f"expected {self.nlocal} tensors, got {len(x)}")
+        return x
+
+    def _ret(self, like: TensorOrList, out: List[torch.Tensor]):
+        return out[0] if isinstance(like, torch.Tensor) else out
+
+    @staticmethod
+    def _aligned(t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        if t.data_ptr() % 16:
+            t = t.clone()
+        return t
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: str = "auto", *, ctas: int = 0,
+                   warps: int = 0, flags: int = 0):
+        """Sum over ranks.  In place unless `out` is given.  Stream-ordered on the current stream."""
+        ins = self._lists(x)
+        outs = ins if out is None else self._lists(out)
+        fixed_in = [self._aligned(t) for t in ins]
+        fixed_out = [o if (o.is_contiguous() and o.data_ptr() % 16 == 0) else torch.empty_like(o, memory_format=torch.contiguous_format)
+                     for o in outs]
+        if out is None:
+            fixed_out = [fi if fi is i else fi for fi, i in zip(fixed_in, ins)]
+        v = torch.ops.b200ipc.all_reduce(fixed_in, fixed_out, self._h, algo, ctas, warps, flags)
+        for o, f in zip(outs, fixed_out):
+            if o is not f:
+                o.copy_(f)
+        self.last_info = CollInfo.from_vec(v)
+        return self._ret(x, outs)
+
+    def all_gather(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: str = "allgather_auto", *,
+                   ctas: int = 0, warps: int = 0, flags: int = 0):
+        """Rank-ordered concatenation along dim 0."""
+        ins = [self._aligned(t) for t in self._lists(x)]
+        if out is None:
+            outs = [torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device) for t in ins]
+        else:
+            outs = self._lists(out)
+        v = torch.ops.b200ipc.all_gather(ins, outs, self._h, algo, ctas, warps, flags)
+        self.last_info = CollInfo.from_vec(v)
+        return self._ret(x, outs)
+
+    def reduce_scatter(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: str = "auto", *, ctas: int = 0,
+                       flags: int = 0):
+        """Sum over ranks; rank r keeps the r-th of `world` equal slices along dim 0."""
+        ins = [self._aligned(t) for t in self._lists(x)]
+        if out is None:
+            outs = [torch.empty((t.shape[0] // self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device) for t in ins]
+        else:
+            outs = self._lists(out)
+        v = torch.ops.b200ipc.reduce_scatter(ins, outs, self._h, algo, ctas, flags)
+        self.last_info = CollInfo.from_vec(v)
+        return self._ret(x, outs)
+
+    def allreduce_residual_rmsnorm(self, x: TensorOrList, residual: TensorOrList, gamma: TensorOrList, eps: float = 1e-5,
+                                   *, ctas: int = 0):
+        """Returns (RMSNorm(all_reduce(x) + residual) * gamma, all_reduce(x) + residual) from one kernel."""
+        xs = self._lists(x)
+        rs = self._lists(residual)
+        gs = self._lists(gamma)
+        xs2 = [t.reshape(-1, t.shape[-1]) for t in xs]
+        rs2 = [t.reshape(-1, t.shape[-1]) for t in rs]
+        outs = [torch.empty_like(t) for t in xs2]
+        res_outs = [torch.empty_like(t) for t in xs2]
+        v = torch.ops.b200ipc.fused_ar_rmsnorm(xs2, rs2, gs, outs, res_outs, eps, self._h, ctas)
+        self.last_info = CollInfo.from_vec(v)
+        outs = [o.view(t.shape) for o, t in zip(outs, xs)]
+        res_outs = [o.view(t.shape) for o, t in zip(res_outs, xs)]
+        return self._ret(x, outs), self._ret(x, res_outs)
+
+    def allreduce_scale_cast(self, x: TensorOrList, scale: float = 1.0, dtype: Optional[torch.dtype] = None, *,
+                             ctas: int = 0):
+        """cast(all_reduce(x) * scale) from one kernel."""
+        xs = [self._aligned(t) for t in self._lists(x)]
+        outs = [torch.empty_like(t, dtype=dtype or t.dtype) for t in xs]
+        v = torch.ops.b200ipc.fused_ar_scale_cast(xs, outs, scale, self._h, ctas)
+        self.last_info = CollInfo.from_vec(v)
+        return self._ret(x, outs)
+
+    # ------------------------------------------------------------------ symmetric memory
+    def empty(self, shape, dtype=torch.float16):
+        """A tensor inside the symmetric heap (same offset on every rank): the large-message
+        collectives then work on it without staging.  Every rank must allocate in the same order."""
+        shape = list(shape) if not isinstance(shape, int) else [shape]
+        ts = [self._C.sym_empty(self._h, shape, dtype, i) for i in range(self.nlocal)]
+        return ts if self._virtual else ts[0]
+
+    def free_symmetric(self):
+        self._C.sym_free_all(self._h)
+
+    # ------------------------------------------------------------------ state
+    @property
+    def has_nvls(self) -> bool:
+        return self._C.has_nvls(self._h)
+
+    @property
+    def nvls_note(self) -> str:
+        return self._C.nvls_note(self._h)
+
+    @property
+    def backing(self) -> str:
+        return self._C.backing(self._h)
+
+    @property
+    def launches(self) -> int:
+        return self._C.launches(self._h)
+
+    def status(self, local: int = 0):
+        keys = ("code", "rank", "peer", "wire", "step", "expected", "seen", "where")
+        return dict(zip(keys, self._C.status(self._h, local)))
+
+    def check(self):
+        """Raises CollectiveError if any finished collective recorded a failure.  Call after a stream sync."""
+        try:
+            self._C.raise_if_failed(self._h)
+        except RuntimeError as e:
+            raise CollectiveError(str(e)) from None
+
+    def reset(self):
+        self._C.reset(self._h)
+
+    def barrier(self):
+        self._C.host_barrier(self._h)
+
+    def set_timeout_ms(self, ms: int):
+        self._C.set_timeout_ms(self._h, ms)
+
+    def set_thresholds(self, oneshot_max_bytes: int, ll_max_bytes: int):
+        self._C.set_thresholds(self._h, oneshot_max_bytes, ll_max_bytes)
+
+    def set_seq(self, seq: int):
+        self._C.set_seq(self._h, seq)
+
+    @property
+    def seq(self) -> int:
+        return self._C.seq(self._h)
+
+    def heap_layout(self):
+        keys = ("ctrl_off", "scatter_off", "gather_off", "half_bytes", "oneshot_off", "oneshot_bytes", "staging_off",
+                "staging_bytes", "total_bytes")
+        return dict(zip(keys, self._C.heap_layout(self._h)))
+
+    def dump_heap(self, offset: int, nbytes: int, local: int = 0) -> torch.Tensor:
+        """Host copy of a piece of this rank's heap (debug view of the scratch rings)."""
+        return self._C.dump_heap(self._h, local, offset, nbytes)
