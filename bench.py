@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Headline benchmark: fp16 all-reduce bus bandwidth (and small-message latency) vs NCCL.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl nccl --gpus N ...                 # NCCL on the same box, same loop
+    python bench.py --impl reference ...                     # the reference (not runnable here)
+
+For N > 1 run it under `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...`
+(one rank per GPU); when started without a launcher's environment it re-launches itself that way.
+With N = 1 there is no peer, so the world is emulated: 8 ranks on the one GPU, one cooperative
+launch per all-reduce, "peer" traffic through L2/HBM instead of NVLink - the same kernels and
+protocol, a different wire.  That is stated in `config.parallelism`.
+
+A step is one all-reduce of the reference's default problem: 8 Mi fp16 elements (16 MiB) per rank
+(`-n 8MB`, main.cpp:179, 45).  Rank 0 prints one JSON line; `value` is the NCCL-convention bus
+bandwidth, busbw = bytes / time * 2 (n-1) / n, from device-side timing (CUDA events on the launching
+stream, max over ranks).  Successive steps use different buffers whose total exceeds L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+METRIC = "fp16_allreduce_busbw_GBps"
+DEFAULT_NELEMS = 8 * 1024 * 1024
+L2_BYTES = 126 << 20
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "nccl", "reference"])
+    p.add_argument("--nelems", type=int, default=DEFAULT_NELEMS)
+    p.add_argument("--algo", default="auto")
+    p.add_argument("--virtual-world", type=int, default=8, help="ranks emulated on one GPU when --gpus 1")
+    p.add_argument("--no-sweep", action="store_true", help="skip the size sweep / NCCL comparison extras")
+    p.add_argument("--no-nvls", action="store_true")
+    return p.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region is timed."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        self.proc.terminate()  # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def busbw(nbytes: int, seconds: float, world: int) -> float:
+    return nbytes / seconds * 2 * (world - 1) / world / 1e9
+
+
+# ---------------------------------------------------------------------------------------------
+def relaunch_under_torchrun(args):
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+    return subprocess.call(cmd)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        # The reference is SYCL + Level Zero + Intel vISA inline assembly built by icpx for Intel GPUs
+        # (Makefile:1-42); it has no Python packaging, no CUDA path for sm_100 and needs MPI.
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "reference is Intel-only SYCL/Level Zero/vISA code with no setup.py or pyproject.toml; "
+                          "pip reports 'not installable' and no SYCL compiler or MPI exists on this image"}))
+        return 0
+    if args.gpus > 1 and "RANK" not in os.environ:
+        return relaunch_under_torchrun(args)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    multi = world > 1
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    n = args.nelems
+    nbytes = n * 2
+    nbuf = max(2, (2 * L2_BYTES + nbytes - 1) // nbytes)  # rotate over > 2x L2 of buffers
+    nbuf = min(nbuf, 32)
+    steps, warmup = args.steps, max(3, args.warmup)
+
+    from gpu_ipc_example_b200 import Communicator
+
+    emu_world = args.virtual_world if not multi else world
+    comm = None
+    if args.impl == "ours":
+        staging = nbuf * nbytes + (64 << 20) + (0 if args.no_sweep else (2 << 26) * 2 * 2 + (64 << 20))
+        if multi:
+            comm = Communicator.from_torch_distributed(local, staging_bytes=staging, nvls=not args.no_nvls)
+        else:
+            comm = Communicator.virtual(emu_world, local, staging_bytes=staging)
+
+    def make_bufs():
+        if args.impl == "ours":
+            bufs = [comm.empty([n], torch.float16) for _ in range(nbuf)]  # symmetric: no staging copy
+        else:
+            bufs = [torch.empty(n, dtype=torch.float16, device="cuda") for _ in range(nbuf)]
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        for b in bufs:
+            for t in (b if isinstance(b, list) else [b]):
+                t.copy_((torch.randn(n, device="cuda", generator=g) * 1e-3).half())
+        return bufs
+
+    bufs = make_bufs()
+
+    def step(i):
+        b = bufs[i % nbuf]
+        if args.impl == "ours":
+            comm.all_reduce(b, None, args.algo)
+        else:
+            if multi:
+                dist.all_reduce(b)
+            else:
+                b.add_(0)  # a world of one: NCCL has nothing to do
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, k):
+        """k calls of fn between barriers; device time in seconds, max over ranks."""
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(k):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / 1e3], device="cuda", dtype=torch.float64)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sync_all()
+        return float(t.item())
+
+    for i in range(warmup):
+        step(i)
+    sync_all()
+    if comm is not None:
+        comm.check()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = comm.launches if comm is not None else 0
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    seconds = timed(step, steps)
+    # keep the GPU busy a little longer so that the 100 ms sampler sees the loaded clocks
+    t_end = time.time() + 0.6
+    extra = 0
+    while time.time() < t_end:
+        step(extra)
+        extra += 1
+        if extra % 16 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    launches = (comm.launches - launches0 - extra) if comm is not None else 0
+    if comm is not None:
+        comm.check()
+    ms_per_step = seconds / steps * 1e3
+    headline_algo = (comm.last_info.sched + ":" + comm.last_info.proto) if comm is not None else "nccl"
+    value = busbw(nbytes, seconds / steps, emu_world)
+
+    # ---- end to end through the public API: pinned host -> device, all-reduce, device -> host --------
+    e2e = None
+    if args.impl == "ours":
+        host_in = [torch.empty(n, dtype=torch.float16).pin_memory() for _ in range(2)]
+        for h in host_in:
+            h.normal_(0, 1e-3)
+        host_out = torch.empty(1024, dtype=torch.float16).pin_memory()
+
+        def e2e_step(i):
+            b = bufs[i % nbuf]
+            first = b[0] if isinstance(b, list) else b
+            if isinstance(b, list):
+                for t in b:
+                    t.copy_(host_in[i % 2], non_blocking=True)
+            else:
+                b.copy_(host_in[i % 2], non_blocking=True)
+            comm.all_reduce(b, None, args.algo)
+            host_out.copy_(first[:1024], non_blocking=True)
+
+        for i in range(3):
+            e2e_step(i)
+        s2 = timed(e2e_step, steps)
+        h2d = nbytes * (emu_world if not multi else 1)
+        e2e = {"value": round(busbw(nbytes, s2 / steps, emu_world), 3), "unit": "GB/s", "ms_per_step": round(s2 / steps * 1e3, 5),
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 2048}
+
+    # ---- extras: small-message latency and a few sizes, ours vs NCCL, outside the headline region ----
+    sweep = None
+    if not args.no_sweep and args.impl == "ours":
+        sweep = []
+        for e in (10, 12, 14, 16, 18, 20, 22, 24, 26):
+            m = 1 << e
+            if m <= n:  # slices of the symmetric buffers (same offset on every rank)
+                views = [[t[:m] for t in b] if isinstance(b, list) else b[:m] for b in bufs]
+            else:
+                views = [comm.empty([m], torch.float16) for _ in range(2)]
+            reps = 200 if e <= 18 else (50 if e <= 22 else 20)
+
+            def ours_step(i, views=views):
+                comm.all_reduce(views[i % len(views)], None, args.algo)
+
+            for i in range(5):
+                ours_step(i)
+            t_ours = timed(ours_step, reps) / reps
+            row = {"elements": m, "bytes": m * 2, "algo": comm.last_info.sched + ":" + comm.last_info.proto,
+                   "ours_us": round(t_ours * 1e6, 3), "ours_busbw": round(busbw(m * 2, t_ours, emu_world), 3)}
+            if multi:
+                tv = [torch.zeros(m, dtype=torch.float16, device="cuda") for _ in range(4)]
+
+                def nccl_step(i, tv=tv):
+                    dist.all_reduce(tv[i % 4])
+
+                for i in range(5):
+                    nccl_step(i)
+                t_nccl = timed(nccl_step, reps) / reps
+                row["nccl_us"] = round(t_nccl * 1e6, 3)
+                row["nccl_busbw"] = round(busbw(m * 2, t_nccl, world), 3)
+            sweep.append(row)
+        comm.check()
+
+    if rank == 0:
+        out = {
+            "metric": METRIC,
+            "value": round(value, 3),
+            "unit": "GB/s",
+            "n_gpus": args.gpus,
+            "steps": steps,
+            "warmup": warmup,
+            "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "fp16",
+            "data": "synthetic N(0,1e-3) seeded by rank",
+            "impl": args.impl,
+            "config": {
+                "model": f"all-reduce of {n} fp16 elements ({nbytes >> 20} MiB) per rank, the reference's default -n 8MB problem",
+                "global_batch": emu_world,
+                "seq_len": n,
+                "parallelism": (f"{world} GPUs, one rank per GPU over NVLink" if multi
+                                else f"{emu_world} ranks emulated on 1 GPU (one cooperative launch; peer traffic stays in L2/HBM, no NVLink)"),
+                "algo": f"{args.algo} -> {headline_algo}",
+                "buffers": f"{nbuf} rotating buffers = {nbuf * nbytes >> 20} MiB > 126 MiB L2, in place, symmetric heap (no staging copy)",
+                "busbw": "bytes/time*2(n-1)/n, device time by CUDA events, max over ranks",
+            },
+            "clocks": clocks,
+            "gpu_launches": launches,
+        }
+        if e2e:
+            out["e2e"] = e2e
+        if sweep:
+            out["sweep"] = sweep
+        if comm is not None and multi:
+            out["config"]["nvls"] = comm.nvls_note
+            out["config"]["backing"] = comm.backing
+        print(json.dumps(out))
+        sys.stdout.flush()
+    if comm is not None:
+        comm.close()
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

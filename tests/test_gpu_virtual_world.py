@@ -161,7 +161,7 @@ def test_many_launches_keep_flags_in_step(comm):
 
 
 def test_sequence_wrap_resets_the_rings(comm):
-    comm.set_seq(0xFFFFFFF0)
+    comm.set_seq(0xFFFFFFFA)
     for _ in range(6):
         _check_allreduce(comm, "simple_pcie_p", 65536, torch.float16)
     assert comm.seq < 0x80000000
