@@ -176,7 +176,10 @@ def main():
     def step(i):
         b = bufs[i % nbuf]
         if args.impl == "ours":
-            comm.all_reduce(b, None, args.algo)
+            if multi:
+                comm.all_reduce_(b, args.algo)
+            else:
+                comm.all_reduce(b, None, args.algo)
         else:
             if multi:
                 dist.all_reduce(b)
@@ -230,6 +233,8 @@ def main():
     if comm is not None:
         comm.check()
     ms_per_step = seconds / steps * 1e3
+    if comm is not None:
+        comm.all_reduce(bufs[0], None, args.algo)  # the reporting path, to learn which algorithm ran
     headline_algo = (comm.last_info.sched + ":" + comm.last_info.proto) if comm is not None else "nccl"
     value = busbw(nbytes, seconds / steps, emu_world)
 
@@ -272,11 +277,15 @@ def main():
             reps = 200 if e <= 18 else (50 if e <= 22 else 20)
 
             def ours_step(i, views=views):
-                comm.all_reduce(views[i % len(views)], None, args.algo)
+                if multi:
+                    comm.all_reduce_(views[i % len(views)], args.algo)
+                else:
+                    comm.all_reduce(views[i % len(views)], None, args.algo)
 
             for i in range(5):
                 ours_step(i)
             t_ours = timed(ours_step, reps) / reps
+            comm.all_reduce(views[0], None, args.algo)  # the reporting path, to learn which algorithm ran
             row = {"elements": m, "bytes": m * 2, "algo": comm.last_info.sched + ":" + comm.last_info.proto,
                    "ours_us": round(t_ours * 1e6, 3), "ours_busbw": round(busbw(m * 2, t_ours, emu_world), 3)}
             if multi:

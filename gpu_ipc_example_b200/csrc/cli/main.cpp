@@ -29,6 +29,7 @@
 #include "../common/check.h"
 #include "../mem/device_registry.h"
 #include "../proto/wire_format.h"
+#include "nccl_baseline.h"
 
 using namespace b200ipc;
 
@@ -58,6 +59,8 @@ struct Options {
   size_t staging_mb = 256;
   bool random = false;
   std::string backing = "auto";
+  std::string baseline;  // "nccl": time NCCL instead of this library
+  bool symmetric = false;
 };
 
 // "8M" -> 8 * 1024 * 1024 elements (main.cpp:17-34; a trailing B as in the default "8MB" is accepted).
@@ -93,7 +96,9 @@ void usage() {
       "      --sweep LO:HI   time 2^LO .. 2^HI elements\n"
       "      --timeout-ms T  budget of one device-side wait (default 2000)\n"
       "      --staging-mb M  staging region of the heap (default 256)\n"
-      "      --backing B     auto | vmm-fd | cuda-ipc | host-shm\n",
+      "      --backing B     auto | vmm-fd | cuda-ipc | host-shm\n"
+      "      --symmetric     buffers inside the symmetric heap (zero-copy for bulk / nvls)\n"
+      "      --baseline nccl time ncclAllReduce / ncclAllGather on the same buffers instead\n",
       algo_names_help().c_str());
 }
 
@@ -120,6 +125,8 @@ bool parse(int argc, char** argv, Options* o) {
                               {"staging-mb", required_argument, nullptr, 1007},
                               {"random", no_argument, nullptr, 1008},
                               {"backing", required_argument, nullptr, 1009},
+                              {"baseline", required_argument, nullptr, 1010},
+                              {"symmetric", no_argument, nullptr, 1011},
                               {"help", no_argument, nullptr, 'h'},
                               {nullptr, 0, nullptr, 0}};
   opterr = 0;  // unknown options are ignored, as in the reference (main.cpp:176)
@@ -148,6 +155,8 @@ bool parse(int argc, char** argv, Options* o) {
       case 1007: o->staging_mb = std::strtoull(optarg, nullptr, 0); break;
       case 1008: o->random = true; break;
       case 1009: o->backing = optarg; break;
+      case 1010: o->baseline = optarg; break;
+      case 1011: o->symmetric = true; break;
       case 'h': usage(); return false;
       default: break;
     }
@@ -181,8 +190,24 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
   const int device = device_for_rank(opt.devices, virt ? 0 : rank, ndev);
   B200_CUDA_CHECK(cudaSetDevice(device));
 
+  std::vector<size_t> sizes;
+  if (!opt.sweep.empty()) {
+    int lo = 10, hi = 24;
+    if (std::sscanf(opt.sweep.c_str(), "%d:%d", &lo, &hi) != 2) B200_REQUIRE(false, "--sweep wants LO:HI");
+    for (int e = lo; e <= hi; ++e) sizes.push_back(size_t(1) << e);
+    if (opt.iters == 1) const_cast<Options&>(opt).iters = 20;
+  } else {
+    sizes.push_back(parse_nelems(opt.nelems));
+  }
+  const size_t max_n = *std::max_element(sizes.begin(), sizes.end());
+  const size_t in_elems = max_n;
+  const size_t out_elems = is_ag ? max_n * size_t(world) : max_n;
+
   CommOptions co;
   co.heap.staging_bytes = opt.staging_mb << 20;
+  // room for the symmetric buffers and for staging the largest message
+  const size_t want_staging = (in_elems + out_elems) * 2 * (opt.symmetric ? 2 : 1) + (size_t(64) << 20);
+  if (co.heap.staging_bytes < want_staging) co.heap.staging_bytes = want_staging;
   co.heap.nvls = opt.nvls;
   co.timeout_ms = opt.timeout_ms;
   co.first_seq = opt.flag;
@@ -197,6 +222,12 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
                 backing_name(comm->heap(0).backing()), comm->has_nvls() ? "on" : (opt.nvls ? comm->heap(0).nvls_note().c_str() : "off"),
                 dt == DType::F16 ? "half" : "bf16", opt.algo.c_str());
   }
+  std::unique_ptr<NcclBaseline> nccl;
+  if (opt.baseline == "nccl") {
+    B200_REQUIRE(mesh != nullptr && world > 1, "--baseline nccl needs a multi-process world");
+    nccl = std::make_unique<NcclBaseline>(*mesh, device);
+    if (rank == 0) std::printf("# baseline: NCCL %d\n", nccl->version());
+  }
   const int nlocal = comm->nlocal();
   const uint32_t flags = opt.ref_accum ? uint32_t(kRoundEachAdd) : 0u;
   cudaStream_t stream;
@@ -205,26 +236,23 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
   B200_CUDA_CHECK(cudaEventCreate(&ev0));
   B200_CUDA_CHECK(cudaEventCreate(&ev1));
 
-  std::vector<size_t> sizes;
-  if (!opt.sweep.empty()) {
-    int lo = 10, hi = 24;
-    if (std::sscanf(opt.sweep.c_str(), "%d:%d", &lo, &hi) != 2) B200_REQUIRE(false, "--sweep wants LO:HI");
-    for (int e = lo; e <= hi; ++e) sizes.push_back(size_t(1) << e);
-  } else {
-    sizes.push_back(parse_nelems(opt.nelems));
-  }
-  const size_t max_n = *std::max_element(sizes.begin(), sizes.end());
-  const size_t in_elems = max_n;
-  const size_t out_elems = is_ag ? max_n * size_t(world) : max_n;
-
   Buffers buf;
   std::vector<std::vector<uint16_t>> host_in(static_cast<size_t>(world));
+  // --symmetric: the buffers live in the heap at the same offset on every rank, so the
+  // large-message kernels work on them in place (no staging copies).
+  size_t sym_in_off = 0, sym_out_off = 0;
+  if (opt.symmetric) {
+    sym_in_off = comm->sym_alloc(in_elems * 2);
+    if (is_ag || opt.out_of_place) sym_out_off = comm->sym_alloc(out_elems * 2);
+  }
   for (int i = 0; i < nlocal; ++i) {
     void *a = nullptr, *b = nullptr;
-    B200_CUDA_CHECK(cudaMalloc(&a, in_elems * 2));
+    if (opt.symmetric) a = comm->sym_ptr(sym_in_off, i);
+    else B200_CUDA_CHECK(cudaMalloc(&a, in_elems * 2));
     buf.in.push_back(a);
     if (is_ag || opt.out_of_place) {
-      B200_CUDA_CHECK(cudaMalloc(&b, out_elems * 2));
+      if (opt.symmetric) b = comm->sym_ptr(sym_out_off, i);
+      else B200_CUDA_CHECK(cudaMalloc(&b, out_elems * 2));
       B200_CUDA_CHECK(cudaMemset(b, 1, out_elems * 2));
       buf.out.push_back(b);
     } else {
@@ -233,7 +261,7 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
   }
   auto cleanup = make_guard([&] {
     cudaDeviceSynchronize();
-    for (int i = 0; i < nlocal; ++i) {
+    for (int i = 0; i < nlocal && !opt.symmetric; ++i) {
       if (buf.out[size_t(i)] != buf.in[size_t(i)]) cudaFree(buf.out[size_t(i)]);
       cudaFree(buf.in[size_t(i)]);
     }
@@ -259,6 +287,11 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
     auto launch_once = [&]() -> CollInfo {
       std::vector<const void*> ins(buf.in.begin(), buf.in.end());
       LaunchGeom g{opt.groups, opt.subgroups};
+      if (nccl) {
+        if (is_ag) nccl->all_gather(ins[0], buf.out[0], n, dt == DType::F16 ? 0 : 1, stream);
+        else nccl->all_reduce(ins[0], buf.out[0], n, dt == DType::F16 ? 0 : 1, stream);
+        return CollInfo{};
+      }
       if (is_ag) return comm->all_gather(algo, dt, ins.data(), buf.out.data(), n, g, stream, flags);
       return comm->all_reduce(algo, dt, ins.data(), buf.out.data(), n, g, stream, flags);
     };

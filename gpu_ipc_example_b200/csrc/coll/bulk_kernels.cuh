@@ -12,6 +12,7 @@
 #pragma once
 
 #include "../proto/dev_backend.cuh"
+#include "kernel_table.h"
 
 namespace b200ipc {
 
@@ -158,7 +159,7 @@ template <typename T, int N, bool NVLS, BulkMode M>
 __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constant__ KArgs args) {
   const RankView& me = args.v[blockIdx.y];
   const HeapLayout& lay = args.lay;
-  constexpr int kU = (N >= 8) ? 2 : 4;
+  constexpr int kU = bulk_unroll(N, NVLS);
   const int tid = int(threadIdx.x);
   const int nthreads = int(blockDim.x);
   const int G = int(gridDim.x);

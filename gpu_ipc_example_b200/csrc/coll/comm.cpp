@@ -516,9 +516,13 @@ CollInfo Comm::launch_bulk(BulkModeId mode, bool nvls, DType t, const void* cons
   const int threads = kBulkThreadsPerCta;
   int cap = std::min(resident_ctas(fn, threads, 0), kMaxBarrierCtas);
   B200_REQUIRE(cap >= 1, "bulk kernel does not fit on the device");
-  const int kU = N >= 8 ? 2 : 4;
+  const int kU = bulk_unroll(N, nvls);
   const int64_t tile_vec = int64_t(kU) * threads;
-  int ctas = geom.ctas > 0 ? geom.ctas : int(std::min<int64_t>(cap, std::max<int64_t>(1, cdiv(shard_vec, tile_vec))));
+  // Spread the tiles evenly: with T tiles and room for `cap` CTAs, every CTA gets
+  // ceil(T / cap) tiles (a grid of `cap` would leave some CTAs with one tile more).
+  const int64_t ntiles = std::max<int64_t>(1, cdiv(shard_vec, tile_vec));
+  const int64_t rounds = cdiv(ntiles, cap);
+  int ctas = geom.ctas > 0 ? geom.ctas : int(cdiv(ntiles, rounds));
   B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs but only " << cap << " can be resident");
 
   KArgs args;
@@ -561,7 +565,9 @@ AlgoSpec Comm::choose_all_reduce(size_t bytes) const {
     a.sched = SchedKind::Parallel;
     a.proto = ProtoKind::LL512;
   } else {
-    a.sched = has_nvls() ? SchedKind::Nvls : SchedKind::Bulk;
+    // In-switch reduction moves (1 + 1/n) S per GPU against 2 (n-1)/n S for the
+    // peer-to-peer form: it wins from four ranks up, loses at two.
+    a.sched = (has_nvls() && world_ >= nvls_min_world_) ? SchedKind::Nvls : SchedKind::Bulk;
     a.proto = ProtoKind::LL512;
   }
   return a;

@@ -161,6 +161,7 @@ class Comm {
   size_t last_sym_off_ = 0;
   size_t oneshot_max_bytes_ = size_t(32) << 10;
   size_t ll_max_bytes_ = size_t(1) << 20;
+  int nvls_min_world_ = 4;
   uint64_t launches_ = 0;
   std::map<std::pair<const void*, int>, int> occupancy_cache_;
 };
