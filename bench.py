@@ -131,6 +131,12 @@ def main():
     if args.gpus > 1 and "RANK" not in os.environ:
         return relaunch_under_torchrun(args)
 
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
+    # there.  Keep the real stdout for that line and point fd 1 at stderr for everything else.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -337,8 +343,8 @@ def main():
         if comm is not None and multi:
             out["config"]["nvls"] = comm.nvls_note
             out["config"]["backing"] = comm.backing
-        print(json.dumps(out))
-        sys.stdout.flush()
+        json_out.write(json.dumps(out) + "\n")
+        json_out.flush()
     if comm is not None:
         comm.close()
     if multi:

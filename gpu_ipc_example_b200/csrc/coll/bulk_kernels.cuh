@@ -194,8 +194,9 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
     int64_t v = nelems - int64_t(s) * shard_elems;
     return v < 0 ? 0 : (v > shard_elems ? shard_elems : v);
   };
-  const int64_t tile_vec = int64_t(kU) * nthreads;
-  const int64_t ntiles = (shard_vec + tile_vec - 1) / tile_vec;
+  // A slab is blockDim consecutive vectors; slab j belongs to CTA j % gridDim.x on every rank
+  // and a CTA keeps kU of its slabs in flight.
+  const int64_t ntiles = (shard_vec + nthreads - 1) / nthreads;
 
   char* my_buf = me.heap + sym_off;
   const uint16_t* in16 = static_cast<const uint16_t*>(me.in);
@@ -205,10 +206,10 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
   if (M != BulkMode::AllGather && copy_in) {
     for (int s = 0; s < N; ++s) {
       const int64_t nv = valid(s);
-      for (int64_t tile = b; tile < ntiles; tile += G)
+      for (int64_t tile = b; tile < ntiles; tile += int64_t(G) * kU)
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-          const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+          const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
           if (i < shard_vec && i * 8 < nv)
             *reinterpret_cast<uint4*>(my_buf + (int64_t(s) * shard_vec + i) * 16) =
                 ld_vec_guarded(in16 + int64_t(s) * shard_elems, i, nv);
@@ -222,16 +223,16 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
   // ---- phase 1: the collective ---------------------------------------------------
   if (M == BulkMode::AllGather) {
     const uint16_t* src16 = copy_in ? in16 : reinterpret_cast<const uint16_t*>(my_buf + int64_t(r) * shard_vec * 16);
-    for (int64_t tile = b; tile < ntiles; tile += G) {
+    for (int64_t tile = b; tile < ntiles; tile += int64_t(G) * kU) {
       uint4 v[kU];
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+        const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
         if (i < shard_vec) v[u] = ld_vec_guarded(src16, i, shard_elems);
       }
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+        const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
         if (i >= shard_vec) continue;
         const size_t off = sym_off + size_t(int64_t(r) * shard_vec + i) * 16;
         if (me.flags & kMuteSends) continue;
@@ -248,12 +249,12 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
       }
     }
   } else {
-    for (int64_t tile = b; tile < ntiles; tile += G) {
+    for (int64_t tile = b; tile < ntiles; tile += int64_t(G) * kU) {
       uint4 res[kU];
       if (NVLS) {
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-          const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+          const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
           if (i < shard_vec)
             res[u] = multimem_ld_reduce_add<T>(me.mc + sym_off + size_t(int64_t(r) * shard_vec + i) * 16);
         }
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
         uint4 v[kU][N];
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-          const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+          const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
           if (i < shard_vec) {
             const size_t off = sym_off + size_t(int64_t(r) * shard_vec + i) * 16;
 #pragma unroll
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
       }
 #pragma unroll
       for (int u = 0; u < kU; ++u) {
-        const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+        const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
         if (i >= shard_vec) continue;
         if (M == BulkMode::ReduceScatter) {
           st_vec_guarded(out16, i, shard_elems, res[u]);  // my shard only, straight to the caller
@@ -305,10 +306,10 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
   if (M != BulkMode::ReduceScatter && copy_out) {
     for (int s = 0; s < N; ++s) {
       const int64_t nv = valid(s);
-      for (int64_t tile = b; tile < ntiles; tile += G)
+      for (int64_t tile = b; tile < ntiles; tile += int64_t(G) * kU)
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
-          const int64_t i = tile * tile_vec + int64_t(u) * nthreads + tid;
+          const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
           if (i < shard_vec && i * 8 < nv)
             st_vec_guarded(out16 + int64_t(s) * shard_elems, i, nv,
                            *reinterpret_cast<const uint4*>(my_buf + (int64_t(s) * shard_vec + i) * 16));

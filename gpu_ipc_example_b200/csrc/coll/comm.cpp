@@ -9,6 +9,7 @@
 #include "../common/check.h"
 #include "../proto/wire_format.h"
 #include "schedules.h"
+#include "tuner.h"
 
 namespace b200ipc {
 
@@ -516,8 +517,7 @@ CollInfo Comm::launch_bulk(BulkModeId mode, bool nvls, DType t, const void* cons
   const int threads = kBulkThreadsPerCta;
   int cap = std::min(resident_ctas(fn, threads, 0), kMaxBarrierCtas);
   B200_REQUIRE(cap >= 1, "bulk kernel does not fit on the device");
-  const int kU = bulk_unroll(N, nvls);
-  const int64_t tile_vec = int64_t(kU) * threads;
+  const int64_t tile_vec = int64_t(threads);  // a slab: one vector per thread; a CTA keeps kU slabs in flight
   // Spread the tiles evenly: with T tiles and room for `cap` CTAs, every CTA gets
   // ceil(T / cap) tiles (a grid of `cap` would leave some CTAs with one tile more).
   const int64_t ntiles = std::max<int64_t>(1, cdiv(shard_vec, tile_vec));
@@ -551,25 +551,37 @@ CollInfo Comm::launch_bulk(BulkModeId mode, bool nvls, DType t, const void* cons
 // ----------------------------------------------------------------------------
 // Public collectives
 // ----------------------------------------------------------------------------
-AlgoSpec Comm::choose_all_reduce(size_t bytes) const {
+AlgoSpec Comm::choose_all_reduce(size_t bytes, bool symmetric) const {
   AlgoSpec a;
   if (const char* e = std::getenv("B200IPC_PROTO")) {
     bool ag = false;
     AlgoSpec forced;
     if (parse_algo(e, &forced, &ag) && !ag && !forced.automatic) return forced;
   }
-  if (bytes <= oneshot_max_bytes_) {
-    a.sched = SchedKind::OneShot;
-    a.proto = ProtoKind::LL16;
-  } else if (bytes <= ll_max_bytes_) {
-    a.sched = SchedKind::Parallel;
-    a.proto = ProtoKind::LL512;
-  } else {
-    // In-switch reduction moves (1 + 1/n) S per GPU against 2 (n-1)/n S for the
-    // peer-to-peer form: it wins from four ranks up, loses at two.
-    a.sched = (has_nvls() && world_ >= nvls_min_world_) ? SchedKind::Nvls : SchedKind::Bulk;
-    a.proto = ProtoKind::LL512;
+  if (oneshot_max_bytes_ != 0 || ll_max_bytes_ != 0) {
+    // thresholds set by the caller override the built-in table
+    if (bytes <= oneshot_max_bytes_) {
+      a.sched = SchedKind::OneShot;
+      a.proto = ProtoKind::LL512;
+    } else if (bytes <= ll_max_bytes_) {
+      a.sched = SchedKind::Parallel;
+      a.proto = ProtoKind::LL512;
+    } else {
+      a.sched = (has_nvls() && world_ >= 8) ? SchedKind::Nvls : SchedKind::Bulk;
+      a.proto = ProtoKind::LL512;
+    }
+    return a;
   }
+  int rows = 0;
+  const TuneRow* t = tune_table(world_, symmetric, &rows);
+  for (int i = 0; i < rows; ++i) {
+    if (t[i].max_bytes == 0 || bytes <= t[i].max_bytes) {
+      a.sched = t[i].sched;
+      a.proto = t[i].proto;
+      break;
+    }
+  }
+  if (a.sched == SchedKind::Nvls && !has_nvls()) a.sched = SchedKind::Bulk;
   return a;
 }
 
@@ -583,7 +595,11 @@ CollInfo Comm::all_reduce(AlgoSpec algo, DType t, const void* const* ins, void* 
     info.sched = SchedKind::OneShot;
     return info;
   }
-  if (algo.automatic) algo = choose_all_reduce(nelems * 2);
+  if (algo.automatic) {
+    bool symmetric = true;
+    for (int i = 0; i < nlocal(); ++i) symmetric &= (ins[i] == outs[i]) && sym_offset_of(ins[i], i) != SIZE_MAX;
+    algo = choose_all_reduce(nelems * 2, symmetric);
+  }
   for (int i = 0; i < nlocal(); ++i) {
     B200_REQUIRE((reinterpret_cast<uintptr_t>(ins[i]) & 3) == 0 && (reinterpret_cast<uintptr_t>(outs[i]) & 3) == 0,
                  "buffers must be 4-byte aligned");
@@ -612,7 +628,7 @@ CollInfo Comm::all_gather(AlgoSpec algo, DType t, const void* const* ins, void* 
   if (algo.automatic) {
     algo = AlgoSpec{};
     const size_t bytes = nelems * 2;
-    if (bytes <= ll_max_bytes_ / size_t(world_) || nelems % 8 != 0) {
+    if (bytes <= (size_t(1) << 20) / size_t(world_) || nelems % 8 != 0) {
       algo.sched = SchedKind::Ring;
       algo.proto = ProtoKind::LL512;
       algo.direct_allgather = true;

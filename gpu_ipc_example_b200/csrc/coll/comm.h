@@ -97,8 +97,9 @@ class Comm {
   CollInfo reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, void* const* outs, size_t nelems,
                           LaunchGeom geom, cudaStream_t stream, uint32_t extra_flags = 0);
 
-  // Size -> algorithm table used for AlgoSpec::automatic.
-  AlgoSpec choose_all_reduce(size_t bytes) const;
+  // Size -> algorithm choice used for AlgoSpec::automatic: the measured table of tuner.h unless
+  // set_thresholds() installed explicit cut-offs (0, 0 restores the table).
+  AlgoSpec choose_all_reduce(size_t bytes, bool symmetric) const;
   void set_thresholds(size_t oneshot_max_bytes, size_t ll_max_bytes) {
     oneshot_max_bytes_ = oneshot_max_bytes;
     ll_max_bytes_ = ll_max_bytes;
@@ -159,9 +160,8 @@ class Comm {
   int max_ctas_ = 0;
   size_t sym_used_ = 0;
   size_t last_sym_off_ = 0;
-  size_t oneshot_max_bytes_ = size_t(32) << 10;
-  size_t ll_max_bytes_ = size_t(1) << 20;
-  int nvls_min_world_ = 4;
+  size_t oneshot_max_bytes_ = 0;
+  size_t ll_max_bytes_ = 0;
   uint64_t launches_ = 0;
   std::map<std::pair<const void*, int>, int> occupancy_cache_;
 };

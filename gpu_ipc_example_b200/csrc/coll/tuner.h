@@ -1,0 +1,63 @@
+// Message size -> algorithm table for `auto`, from device-timed sweeps on an
+// 8 x B200 NVSwitch node (2^10 .. 2^28 fp16 elements, worlds of 2, 4 and 8; every
+// schedule x wire format; slowest rank).  Each row is "up to this many bytes use
+// that schedule and wire format"; the last row of a table has no upper bound.
+//
+// What the sweeps showed: one NVLink hop (one-shot) wins while the (n-1) x payload
+// it pushes stays small; the two-phase flag-in-data schedules win up to a few MiB
+// because they read and write the caller's buffers directly and need no barrier;
+// beyond that the barrier-based kernels win - in-switch reduction (NVLS) at eight
+// ranks, peer-to-peer loads and stores at two and four, where NVLS moves no fewer
+// bytes per GPU.  Buffers outside the symmetric heap pay a staging copy in the
+// barrier-based kernels, which moves their break-even up.
+#pragma once
+
+#include <cstddef>
+
+#include "../common/types.h"
+
+namespace b200ipc {
+
+struct TuneRow {
+  size_t max_bytes;  // inclusive upper bound; 0 = no bound
+  SchedKind sched;
+  ProtoKind proto;
+};
+
+constexpr size_t KiB = 1024, MiB = 1024 * 1024;
+
+// `large` is filled in by the caller: Nvls or Bulk depending on what the world supports.
+inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
+  static const TuneRow w8_sym[] = {
+      {128 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {2 * MiB, SchedKind::Bisect, ProtoKind::LL512},      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},
+      {8 * MiB, SchedKind::Ring, ProtoKind::LL512},        {0, SchedKind::Nvls, ProtoKind::LL512}};
+  static const TuneRow w8_user[] = {
+      {128 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {2 * MiB, SchedKind::Bisect, ProtoKind::LL512},      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},
+      {8 * MiB, SchedKind::Ring, ProtoKind::LL512},        {32 * MiB, SchedKind::Sequential, ProtoKind::LL512},
+      {0, SchedKind::Nvls, ProtoKind::LL512}};
+  static const TuneRow w4_sym[] = {
+      {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {8 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {0, SchedKind::Bulk, ProtoKind::LL512}};
+  static const TuneRow w4_user[] = {
+      {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {16 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {0, SchedKind::Bulk, ProtoKind::LL512}};
+  static const TuneRow w2[] = {
+      {64 * KiB, SchedKind::OneShot, ProtoKind::LL512},    {2 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+      {0, SchedKind::Bulk, ProtoKind::LL512}};
+  if (world >= 8) {
+    *rows = symmetric ? 6 : 7;
+    return symmetric ? w8_sym : w8_user;
+  }
+  if (world >= 4) {
+    *rows = 5;
+    return symmetric ? w4_sym : w4_user;
+  }
+  *rows = 3;
+  return w2;
+}
+
+}  // namespace b200ipc

@@ -10,9 +10,16 @@
 #include <torch/extension.h>
 #include <torch/library.h>
 
+#include <sys/mman.h>
+#include <unistd.h>
+
 #include <map>
 #include <memory>
 #include <mutex>
+#include <tuple>
+
+#include "../mem/device_registry.h"
+#include "../proto/wire_format.h"
 
 #include "../bootstrap/unix_mesh.h"
 #include "../coll/comm.h"
@@ -309,6 +316,51 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                 int64_t(l.staging_off),  int64_t(l.staging_bytes), int64_t(l.total_bytes)};
   });
   m.def("algo_names", &algo_names_help);
+  // Parses an algorithm name: (known, is_allgather, automatic, schedule, proto, direct).
+  m.def("parse_algo", [](const std::string& name) {
+    AlgoSpec a;
+    bool ag = false;
+    bool ok = parse_algo(name, &a, &ag);
+    return std::make_tuple(ok, ag, a.automatic, std::string(sched_name(a.sched)), std::string(proto_name(a.proto)),
+                           a.direct_allgather);
+  });
+  // Exercises the bootstrap mesh without a GPU: all-gathers a blob, passes a memfd
+  // whose content is the sender's rank (SCM_RIGHTS), runs a barrier and a max-reduce.
+  // Returns (gathered bytes, ranks read back through the received descriptors, max).
+  m.def("mesh_selftest", [](int64_t rank, int64_t world, const std::string& job, int64_t instance, int64_t timeout_ms,
+                            const std::string& blob) {
+    MeshOptions mo;
+    mo.job_id = job;
+    mo.instance = int(instance);
+    mo.timeout_ms = int(timeout_ms);
+    UnixMesh mesh(int(rank), int(world), mo);
+    std::string all(blob.size() * size_t(world), '\0');
+    mesh.allgather(blob.data(), blob.size(), all.data());
+    int fd = ::memfd_create("b200ipc-selftest", 0);
+    B200_SYS_CHECK(fd);
+    int32_t me = int32_t(rank);
+    B200_SYS_CHECK(::write(fd, &me, sizeof(me)));
+    std::vector<int> fds = mesh.allgather_fds(fd);
+    ::close(fd);
+    std::vector<int64_t> seen;
+    for (int f : fds) {
+      int32_t v = -1;
+      B200_SYS_CHECK(::pread(f, &v, sizeof(v), 0));
+      ::close(f);
+      seen.push_back(v);
+    }
+    mesh.barrier();
+    int64_t mx = mesh.allreduce_max(rank * 10);
+    return std::make_tuple(py::bytes(all), seen, mx);
+  });
+  m.def("rank_env", []() {
+    RankEnv e = rank_env_from_environment();
+    return std::make_tuple(e.found, e.rank, e.world, e.local_rank, e.job_id);
+  });
+  m.def("device_for_rank", [](const std::string& list, int64_t rank, int64_t ndev) {
+    return device_for_rank(list, int(rank), int(ndev));
+  });
+  m.def("describe_devices", &describe_devices);
   m.def("socket_name", [](const std::string& job, int64_t instance, int64_t rank) {
     MeshOptions mo;
     mo.job_id = job;

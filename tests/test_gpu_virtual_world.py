@@ -168,12 +168,19 @@ def test_sequence_wrap_resets_the_rings(comm):
 
 
 def test_auto_picks_by_size(comm):
+    # the built-in table (measured on NVLink) must at least be correct at every size class
+    for n in (1024, 70000, 300000, 1 << 20, 3 << 20):
+        _check_allreduce(comm, "auto", n, torch.float16)
+    assert comm.last_info.sched != "oneshot"
+    # explicit cut-offs override the table
+    comm.set_thresholds(32 << 10, 1 << 20)
     _check_allreduce(comm, "auto", 1024, torch.float16)
     assert comm.last_info.sched == "oneshot"
     _check_allreduce(comm, "auto", 256 * 1024, torch.float16)
     assert comm.last_info.sched == "parallel"
     _check_allreduce(comm, "auto", 2 * 1024 * 1024, torch.float16)
     assert comm.last_info.sched in ("bulk", "nvls")
+    comm.set_thresholds(0, 0)
 
 
 def test_fused_allreduce_residual_rmsnorm(comm):
