@@ -219,6 +219,7 @@ void Comm::reset() {
   // Start a fresh epoch well away from anything that may still sit in a ring.
   seq_ = (seq_ + 0x10000u) | 1u;
   bar_seq_ = 0;
+  gemm_done_ = 0;
   host_barrier();
 }
 
@@ -290,6 +291,17 @@ void Comm::launch(KernelFn fn, int ctas, int threads, KArgs* args, size_t smem, 
     B200_CUDA_CHECK(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), grid, block, params, smem, stream));
   } else {
     B200_CUDA_CHECK(cudaLaunchKernel(reinterpret_cast<const void*>(fn), grid, block, params, smem, stream));
+  }
+  ++launches_;
+}
+
+void Comm::launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream) {
+  dim3 grid(unsigned(ctas), unsigned(nlocal()), 1);
+  dim3 block(unsigned(threads), 1, 1);
+  if (nlocal() > 1) {
+    B200_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream));
+  } else {
+    B200_CUDA_CHECK(cudaLaunchKernel(fn, grid, block, params, smem, stream));
   }
   ++launches_;
 }

@@ -138,6 +138,14 @@ class Comm {
   int resident_ctas(KernelFn fn, int threads, size_t smem);
   uint32_t take_seq(uint32_t advance);
   uint32_t take_barrier();
+  // Launch with caller-built parameters (cooperative when this communicator drives several ranks).
+  void launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream);
+  // Running total of the delivery counter of the fused GEMM kernels: returns the value the
+  // counter reaches after `inc` more deliveries.
+  uint32_t take_done(uint32_t inc) {
+    gemm_done_ += inc;
+    return gemm_done_;
+  }
 
  private:
   Comm() = default;
@@ -155,6 +163,7 @@ class Comm {
   std::vector<StatusBlock*> status_;  // pinned, one per local rank
   uint32_t seq_ = 1;
   uint32_t bar_seq_ = 0;
+  uint32_t gemm_done_ = 0;
   bool device_seq_ = false;
   uint64_t timeout_ns_ = 2000000000ull;
   int max_ctas_ = 0;

@@ -26,3 +26,26 @@ CollInfo fused_allreduce_scale_cast(Comm& comm, DType tin, DType tout, const voi
                                     size_t nelems, float scale, int ctas, cudaStream_t stream);
 
 }  // namespace b200ipc
+
+namespace b200ipc {
+
+// Row-parallel linear layer fused with its all-reduce (and residual-add + RMSNorm): see gemm_ar.cuh.
+struct GemmArPtrs {
+  const void* x;         // [M, K] this rank's activation slice, K contiguous
+  const void* w;         // [N, K] this rank's weight slice (nn.Linear layout), K contiguous
+  const void* residual;  // [M, N] or nullptr
+  const void* gamma;     // [N] or nullptr
+  void* out;             // [M, N] in the symmetric heap
+  void* res_out;         // [M, N] in the symmetric heap, or nullptr
+  void* workspace;       // gemm_ar_workspace() bytes in the symmetric heap, zeroed once before first use
+};
+struct GemmArWorkspace {
+  size_t landing_bytes = 0;
+  size_t flags_bytes = 0;
+  size_t total() const { return landing_bytes + flags_bytes; }
+};
+GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N);
+CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
+                              bool with_norm, int ctas, cudaStream_t stream);
+
+}  // namespace b200ipc

@@ -1,0 +1,131 @@
+#include <algorithm>
+#include <cstring>
+
+#include "../common/check.h"
+#include "../common/cu_driver.h"
+#include "fused_ops.h"
+#include "gemm_ar.cuh"
+
+namespace b200ipc {
+namespace {
+
+constexpr int kStages128 = 6;  // 6 x (16 KiB + 16 KiB) = 192 KiB of the 227 KiB a CTA may use
+constexpr int kStages64 = 8;   // 8 x (16 KiB +  8 KiB) = 192 KiB
+
+template <typename T, int BN, int STAGES>
+const void* kernel_ptr() {
+  return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES>);
+}
+
+void encode_2d(CUtensorMap* map, DType t, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "GEMM operands must be 16-byte aligned");
+  B200_REQUIRE((cols * 2) % 16 == 0, "the K extent must be a multiple of 8 elements");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {uint32_t(kGemmBK), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  B200_CU_CHECK(cu().TensorMapEncodeTiled(map, t == DType::F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                          2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+}
+
+}  // namespace
+
+GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
+  GemmArWorkspace w;
+  const int64_t rpr = (M + world - 1) / world;
+  const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  w.landing_bytes = size_t(world) * size_t(rpr) * size_t(N) * 2;
+  w.landing_bytes = (w.landing_bytes + 255) / 256 * 256;
+  w.flags_bytes = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
+  w.flags_bytes = (w.flags_bytes + 255) / 256 * 256;
+  return w;
+}
+
+CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
+                              bool with_norm, int ctas_req, cudaStream_t stream) {
+  const int W = comm.world();
+  B200_REQUIRE(M > 0 && N > 0 && K > 0, "empty GEMM");
+  B200_REQUIRE(N % 64 == 0, "N must be a multiple of 64");
+  B200_REQUIRE(K % 8 == 0, "K must be a multiple of 8");
+  B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
+  B200_CUDA_CHECK(cudaSetDevice(comm.device()));
+  const bool small_m = M <= 128 || N % 128 != 0;
+  const int BN = small_m ? 64 : 128;
+  const void* fn;
+  size_t smem;
+  if (t == DType::F16) {
+    fn = small_m ? kernel_ptr<__half, 64, kStages64>() : kernel_ptr<__half, 128, kStages128>();
+  } else {
+    fn = small_m ? kernel_ptr<__nv_bfloat16, 64, kStages64>() : kernel_ptr<__nv_bfloat16, 128, kStages128>();
+  }
+  smem = (small_m ? sizeof(GemmSmem<64, kStages64>) : sizeof(GemmSmem<128, kStages128>)) + 1024;
+  B200_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+
+  const int64_t rpr = (M + W - 1) / W;
+  const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const int64_t n_tiles = N / BN;
+  const int64_t total_tiles = m_tiles * n_tiles;
+  int cap = comm.resident_ctas(reinterpret_cast<KernelFn>(const_cast<void*>(fn)), kGemmThreads, smem);
+  B200_REQUIRE(cap >= 1, "GEMM kernel does not fit on the device");
+  int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, std::max<int64_t>(total_tiles, std::min<int64_t>(rpr, cap))));
+  B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs, only " << cap << " can run at once");
+
+  GemmArArgs args;
+  std::memset(&args, 0, sizeof(args));
+  std::vector<const void*> ins(size_t(comm.nlocal()), nullptr);
+  std::vector<void*> outs(size_t(comm.nlocal()), nullptr);
+  comm.fill_views(&args.k, ins.data(), outs.data(), size_t(M * N), 0);
+  const GemmArWorkspace ws = gemm_ar_workspace(W, M, N);
+  size_t landing_off = SIZE_MAX, out_off = SIZE_MAX, res_off = 0;
+  for (int i = 0; i < comm.nlocal(); ++i) {
+    const GemmArPtrs& p = ptrs[i];
+    const size_t lo = comm.sym_offset_of(p.workspace, i);
+    const size_t oo = comm.sym_offset_of(p.out, i);
+    const size_t ro = p.res_out ? comm.sym_offset_of(p.res_out, i) : 0;
+    B200_REQUIRE(lo != SIZE_MAX && oo != SIZE_MAX && ro != SIZE_MAX,
+                 "workspace, out and res_out must be tensors from the symmetric heap (Communicator.empty)");
+    if (i == 0) {
+      landing_off = lo;
+      out_off = oo;
+      res_off = ro;
+    }
+    B200_REQUIRE(lo == landing_off && oo == out_off && ro == res_off, "symmetric tensors must sit at the same offset on every rank");
+    B200_REQUIRE(lo % 256 == 0 && oo % 16 == 0 && ro % 16 == 0, "symmetric tensors must be 16-byte aligned");
+    if (with_norm) B200_REQUIRE(p.gamma != nullptr, "RMSNorm needs gamma");
+    encode_2d(&args.tma_a[i], t, p.x, uint64_t(M), uint64_t(K), kGemmBM);
+    encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(BN));
+    args.residual[i] = p.residual;
+    args.gamma[i] = p.gamma;
+  }
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  args.rows_per_rank = int(rpr);
+  args.eps = eps;
+  args.with_norm = with_norm ? 1 : 0;
+  args.landing_off = landing_off;
+  args.flags_off = landing_off + ws.landing_bytes;
+  args.out_off = out_off;
+  args.res_out_off = res_off;
+  const uint32_t first = comm.take_seq(2);
+  args.done_target = comm.take_done(uint32_t(W) * uint32_t(ctas));
+  for (int i = 0; i < comm.nlocal(); ++i) args.k.v[i].seq = first;
+
+  void* params[] = {&args};
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+
+  CollInfo info;
+  info.sched = SchedKind::Bulk;
+  info.proto = ProtoKind::LL512;
+  info.ctas = ctas;
+  info.warps = kGemmThreads / 32;
+  info.nwires = ctas * kGemmThreads / 32;
+  info.steps = (total_tiles + ctas - 1) / ctas;
+  info.first_flag = first;
+  info.launches = 1;
+  return info;
+}
+
+}  // namespace b200ipc

@@ -1,0 +1,497 @@
+// Row-parallel linear layer fused with its all-reduce and what follows it:
+//
+//     Y = sum over ranks r of  X_r[M, K] . W_r[N, K]^T          (each rank holds a K-slice)
+//     res_out = Y + residual ;  out = RMSNorm(res_out) * gamma   (or out = Y without the norm)
+//
+// in ONE kernel per rank:
+//   1. GEMM on the 5th-generation tensor cores: TMA (cp.async.bulk.tensor, 128-byte
+//      swizzle, no multicast) streams 128 x 64 tiles of X and BN x 64 tiles of W into a
+//      shared-memory ring; one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16)
+//      into a double-buffered fp32 accumulator in tensor memory; four epilogue warps read
+//      it back with tcgen05.ld.
+//   2. Reduce-scatter inside the epilogue: each finished tile is rounded to 16 bit and
+//      stored straight into the memory of the rank that owns those rows (peer stores over
+//      NVLink), then one flag per (source, tile) is released - so the transfer of tile i
+//      overlaps the math of tile i+1.
+//   3. The owner adds the world partial copies of its rows in rank order in fp32, adds the
+//      residual, computes the row statistic, and pushes the normalised rows and the new
+//      residual to every rank (all-gather), again with plain peer stores.
+//   4. A counter per rank tells when every owner has delivered; the kernel ends only then.
+// Rows are owned in contiguous blocks of ceil(M / world).  Every wait is bounded; the
+// waits on peers come after tensor memory has been returned.
+//
+// No counterpart in the reference.  Baseline: cuBLAS GEMM + NCCL all-reduce + a separate
+// add/normalise kernel.
+#pragma once
+
+#include <cuda.h>
+
+#include "../coll/bulk_kernels.cuh"
+#include "../proto/dev_backend.cuh"
+
+namespace b200ipc {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;        // 64 x 2 B = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr uint32_t kMbarSpinLimit = 1u << 24;
+
+struct GemmArArgs {
+  KArgs k;
+  alignas(64) CUtensorMap tma_a[kMaxRanks];  // X  [M, K], K contiguous
+  alignas(64) CUtensorMap tma_b[kMaxRanks];  // W  [N, K], K contiguous (nn.Linear layout)
+  const void* residual[kMaxRanks];           // [M, N] or nullptr
+  const void* gamma[kMaxRanks];              // [N] or nullptr
+  int M, N, K;
+  int rows_per_rank;
+  uint32_t done_target;  // value the local delivery counter reaches when all owners are done
+  float eps;
+  int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
+  // heap offsets (same on every rank)
+  uint64_t landing_off;  // [world][rows_per_rank][N] 16-bit partials
+  uint64_t flags_off;    // [world][m_tiles][n_tiles] uint32
+  uint64_t out_off;      // [M][N]
+  uint64_t res_out_off;  // [M][N] (0 = not wanted)
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up (and tells the whole CTA through *abort_flag) after kMbarSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t n = 0; n < kMbarSpinLimit; ++n) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((n & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 16-bit
+// elements) in the 128-byte swizzle TMA writes: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+  d |= uint64_t(1) << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+  d |= uint64_t(1) << 46;                      // descriptor version of this architecture
+  d |= uint64_t(2) << 61;                      // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: 16-bit A and B (K-major), fp32 accumulate, M x N tile.
+template <typename T>
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+  const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
+  alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float red[8];
+};
+
+template <typename T, int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_constant__ GemmArArgs args) {
+  extern __shared__ unsigned char smem_raw[];
+  using Smem = GemmSmem<BN, STAGES>;
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const RankView& me = args.k.v[blockIdx.y];
+  const HeapLayout& lay = args.k.lay;
+  const int W = me.world;
+  const int rank = me.rank;
+  const int warp = int(threadIdx.x >> 5);
+  const int lane = int(threadIdx.x & 31);
+  const int G = int(gridDim.x);
+  const int M = args.M, N = args.N, K = args.K;
+  const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const int n_tiles = N / BN;
+  const int k_iters = (K + kGemmBK - 1) / kGemmBK;
+  const int total_tiles = m_tiles * n_tiles;
+  const int rpr = args.rows_per_rank;
+  uint32_t seq = me.seq;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  constexpr uint32_t kStageBytes = (kGemmBM + BN) * kGemmBK * 2;
+
+  // ---- set-up ---------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    s.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  // ---- phase 1: GEMM + reduce-scatter epilogue ---------------------------------------------
+  if (warp == 0) {
+    if (lane == 0) {
+      const CUtensorMap* ta = &args.tma_a[blockIdx.y];
+      const CUtensorMap* tb = &args.tma_b[blockIdx.y];
+      uint32_t it = 0;
+      for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G) {
+        const int mt = t / n_tiles, nt = t % n_tiles;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int st = int(it % STAGES);
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag)) break;
+          mbar_expect_tx(&s.full[st], kStageBytes);
+          tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
+          tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
+        }
+      }
+      // copies in flight land in this CTA's shared memory: wait for the ones still pending
+      for (uint32_t back = 0; back < uint32_t(STAGES) && back < it; ++back) {
+        const uint32_t j = it - 1 - back;
+        mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1u, abort_flag);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<T>(kGemmBM, BN);
+      uint32_t it = 0, tile_i = 0;
+      for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
+        const uint32_t buf = tile_i & 1u;
+        const uint32_t use = tile_i >> 1;  // how often this accumulator buffer has been used before
+        if (!mbar_wait(&s.acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        bool ok = true;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int st = int(it % STAGES);
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&s.full[st], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st]));
+          const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st]));
+#pragma unroll
+          for (int k = 0; k < kGemmBK / 16; ++k) {
+            // advance 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
+            umma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&s.empty[st]);  // the stage may be refilled once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&s.acc_full[buf]);  // accumulator complete
+      }
+    }
+  } else {
+    // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
+    const int lane_group = warp & 3;
+    const int row_in_tile = lane_group * 32 + lane;
+    uint32_t tile_i = 0;
+    for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
+      const int mt = t / n_tiles, nt = t % n_tiles;
+      const uint32_t buf = tile_i & 1u;
+      const uint32_t use = tile_i >> 1;
+      if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = mt * kGemmBM + row_in_tile;
+      const int owner = row / rpr;
+      const bool live = row < M && !(me.flags & kMuteSends);
+      // destination: the owner's landing zone, block of this source rank
+      char* dst = nullptr;
+      if (row < M)
+        dst = me.peer[owner] + args.landing_off +
+              ((size_t(rank) * rpr + size_t(row - owner * rpr)) * size_t(N) + size_t(nt) * BN) * 2;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t acc[32];
+        tmem_ld_32cols(tmem_base + (uint32_t(lane_group * 32) << 16) + buf * BN + uint32_t(c), acc);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = Cvt<T>::down(__uint_as_float(acc[8 * v + 0]), __uint_as_float(acc[8 * v + 1]));
+            o.y = Cvt<T>::down(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
+            o.z = Cvt<T>::down(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
+            o.w = Cvt<T>::down(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
+            *reinterpret_cast<uint4*>(dst + (c + 8 * v) * 2) = o;
+          }
+        }
+      }
+      // accumulator buffer free again
+      tc_fence_before_sync();
+      __syncwarp();  // also orders this warp's 32 row stores before the flag stores below
+      if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+      // One flag per (source, tile, 32-row group) on every owner that got rows from this warp:
+      // no barrier between the epilogue warps is needed, each warp answers for its own rows.
+      const int first_row = mt * kGemmBM + lane_group * 32;
+      if (first_row < M && !(me.flags & kMuteSends)) {
+        int last_row = first_row + 31;
+        if (last_row > M - 1) last_row = M - 1;
+        const int q = first_row / rpr + lane;
+        if (q <= last_row / rpr) {
+          __threadfence_system();
+          uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[q] + args.flags_off) +
+                        ((size_t(rank) * m_tiles + mt) * n_tiles + nt) * 4 + lane_group;
+          st_release_sys_u32(f, seq);
+        }
+      }
+    }
+  }
+
+  // ---- tensor memory goes back before anything waits on a peer ---------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (*abort_flag) {
+    if (threadIdx.x == 0) {
+      uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
+      if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+        StatusBlock* sb = me.status;
+        sb->rank = uint32_t(rank);
+        sb->peer = uint32_t(rank);
+        sb->wire = blockIdx.x;
+        sb->where = 20;  // a local pipeline wait (TMA / MMA / epilogue hand-over) gave up
+        __threadfence_system();
+        sb->code = kTimeout;
+        __threadfence_system();
+      }
+    }
+    return;
+  }
+
+  // ---- phase 2/3: owner reduce (+ residual, RMSNorm) and all-gather push ------------------------
+  const int row0 = rank * rpr;
+  int nrows = M - row0;
+  if (nrows > rpr) nrows = rpr;
+  if (nrows < 0) nrows = 0;
+  const int nvec = N / 8;
+  const int nthreads = int(blockDim.x);
+  const uint16_t* residual = static_cast<const uint16_t*>(args.residual[blockIdx.y]);
+  const uint4* gamma = static_cast<const uint4*>(args.gamma[blockIdx.y]);
+  uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+
+  for (int i = int(blockIdx.x); i < nrows; i += G) {
+    const int row = row0 + i;
+    const int mt = row / kGemmBM;
+    // wait for every source's partial tiles of this row (flags live in my own memory)
+    for (int f = int(threadIdx.x); f < W * n_tiles; f += nthreads) {
+      const int src = f / n_tiles, nt = f % n_tiles;
+      const uint32_t* fp = reinterpret_cast<const uint32_t*>(me.heap + args.flags_off) +
+                           ((size_t(src) * m_tiles + mt) * n_tiles + nt) * 4 + (row % kGemmBM) / 32;
+      uint32_t spins = 0;
+      uint64_t t0 = 0;
+      for (;;) {
+        const uint32_t seen = ld_acquire_sys_u32(fp);
+        if (seen == seq) break;
+        if ((++spins & 0x3fu) == 0) {
+          if (ld_volatile_u32(abort_word) != 0 || s_fail) { s_fail = 1; break; }
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > me.timeout_ns) {
+            if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+              StatusBlock* sb = me.status;
+              sb->rank = uint32_t(rank);
+              sb->peer = uint32_t(src);
+              sb->wire = blockIdx.x;
+              sb->step = uint32_t(nt);
+              sb->expected = seq;
+              sb->seen = seen;
+              sb->where = 21;
+              __threadfence_system();
+              sb->code = kTimeout;
+              __threadfence_system();
+            }
+            for (int q = 0; q < W; ++q)
+              if (q != rank) st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[q] + lay.ctrl_off + kCtrlAbortOff), 1u);
+            s_fail = 1;
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (s_fail) break;
+
+    // pass 1: sum the world copies in rank order (+ residual), keep the rounded row locally
+    uint16_t* my_res = reinterpret_cast<uint16_t*>(me.heap + (args.res_out_off ? args.res_out_off : args.out_off)) + size_t(row) * N;
+    float ss = 0.f;
+    for (int v = int(threadIdx.x); v < nvec; v += nthreads) {
+      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int src = 0; src < W; ++src) {
+        const uint4 x = *reinterpret_cast<const uint4*>(me.heap + args.landing_off + ((size_t(src) * rpr + i) * size_t(N)) * 2 + size_t(v) * 16);
+        acc8_add<T>(a, x);
+      }
+      if (residual) acc8_add<T>(a, *reinterpret_cast<const uint4*>(residual + size_t(row) * N + size_t(v) * 8));
+      const uint4 o = acc8_pack<T>(a);
+      *reinterpret_cast<uint4*>(my_res + size_t(v) * 8) = o;
+      if (args.with_norm) {
+        float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        acc8_add<T>(b, o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += b[e] * b[e];
+      }
+    }
+    float inv = 1.f;
+    if (args.with_norm) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s.red[warp] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < nthreads / 32; ++w) tot += s.red[w];
+      inv = rsqrtf(tot / float(N) + args.eps);
+    }
+    __syncthreads();  // my_res written by all threads; s.red consumed
+    // pass 2: normalise and push both rows to every rank
+    for (int v = int(threadIdx.x); v < nvec; v += nthreads) {
+      const uint4 x = *reinterpret_cast<const uint4*>(my_res + size_t(v) * 8);
+      uint4 y = x;
+      if (args.with_norm) {
+        const uint4 g = gamma[v];
+        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+        const uint32_t gs[4] = {g.x, g.y, g.z, g.w};
+        uint32_t ys[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = Cvt<T>::up(xs[e]);
+          const float2 gf = Cvt<T>::up(gs[e]);
+          ys[e] = Cvt<T>::down(xf.x * inv * gf.x, xf.y * inv * gf.y);
+        }
+        y = make_uint4(ys[0], ys[1], ys[2], ys[3]);
+      }
+      if (!(me.flags & kMuteSends)) {
+        for (int k = 0; k < W; ++k) {
+          const int q = (rank + k) % W;
+          *reinterpret_cast<uint4*>(me.peer[q] + args.out_off + (size_t(row) * N + size_t(v) * 8) * 2) = y;
+          if (args.res_out_off && q != rank)
+            *reinterpret_cast<uint4*>(me.peer[q] + args.res_out_off + (size_t(row) * N + size_t(v) * 8) * 2) = x;
+        }
+      }
+    }
+  }
+
+  // ---- phase 4: tell everyone this CTA has delivered; CTA 0 waits for all deliveries ---------------
+  __syncthreads();
+  uint32_t* done = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlSeqOff) + 4;
+  if (threadIdx.x < uint32_t(W) && !(me.flags & kMuteSends) && !s_fail) {
+    __threadfence_system();
+    red_release_sys_add(reinterpret_cast<uint32_t*>(me.peer[threadIdx.x] + lay.ctrl_off + kCtrlSeqOff) + 4, 1u);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && !s_fail) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+      const uint32_t seen = ld_acquire_sys_u32(done);
+      if (int32_t(seen - args.done_target) >= 0) break;
+      if ((++spins & 0x3fu) == 0) {
+        if (ld_volatile_u32(abort_word) != 0) break;
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > me.timeout_ns) {
+          if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+            StatusBlock* sb = me.status;
+            sb->rank = uint32_t(rank);
+            sb->peer = 0;
+            sb->wire = 0;
+            sb->expected = args.done_target;
+            sb->seen = seen;
+            sb->where = 22;
+            __threadfence_system();
+            sb->code = kTimeout;
+            __threadfence_system();
+          }
+          break;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace b200ipc

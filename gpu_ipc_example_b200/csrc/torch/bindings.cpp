@@ -265,9 +265,55 @@ std::vector<int64_t> fused_ar_scale_cast(std::vector<at::Tensor> ins, std::vecto
   return info_vec(info);
 }
 
+// Row-parallel linear + all-reduce (+ residual + RMSNorm).  xs: [M, K] per rank, ws: [N, K] per rank
+// (nn.Linear layout); outs / res_outs / workspaces are symmetric tensors.  residuals / gammas /
+// res_outs may be empty lists.
+std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::Tensor> ws, std::vector<at::Tensor> residuals,
+                                   std::vector<at::Tensor> gammas, std::vector<at::Tensor> outs,
+                                   std::vector<at::Tensor> res_outs, std::vector<at::Tensor> workspaces, double eps,
+                                   bool with_norm, int64_t comm_id, int64_t ctas) {
+  Comm& c = get(comm_id);
+  check_tensors(c, xs, "x");
+  check_tensors(c, ws, "weight");
+  check_tensors(c, outs, "output");
+  check_tensors(c, workspaces, "workspace");
+  if (!residuals.empty()) check_tensors(c, residuals, "residual");
+  if (!gammas.empty()) check_tensors(c, gammas, "gamma");
+  if (!res_outs.empty()) check_tensors(c, res_outs, "residual output");
+  TORCH_CHECK(xs[0].dim() == 2 && ws[0].dim() == 2, "b200ipc: x must be [M, K] and weight [N, K]");
+  const int64_t M = xs[0].size(0), K = xs[0].size(1), N = ws[0].size(0);
+  TORCH_CHECK(ws[0].size(1) == K, "b200ipc: weight must be [N, K] with the same K as x");
+  GemmArWorkspace need = gemm_ar_workspace(c.world(), M, N);
+  std::vector<GemmArPtrs> p(size_t(c.nlocal()));
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(xs[i].sizes() == xs[0].sizes() && ws[i].sizes() == ws[0].sizes() && outs[i].numel() == M * N,
+                "b200ipc: shape mismatch between ranks");
+    TORCH_CHECK(xs[i].scalar_type() == ws[i].scalar_type() && xs[i].scalar_type() == outs[i].scalar_type(), "b200ipc: dtype mismatch");
+    TORCH_CHECK(size_t(workspaces[i].numel() * workspaces[i].element_size()) >= need.total(), "b200ipc: workspace too small, need ",
+                need.total(), " bytes");
+    p[size_t(i)].x = xs[i].data_ptr();
+    p[size_t(i)].w = ws[i].data_ptr();
+    p[size_t(i)].residual = residuals.empty() ? nullptr : residuals[i].data_ptr();
+    p[size_t(i)].gamma = gammas.empty() ? nullptr : gammas[i].data_ptr();
+    p[size_t(i)].out = outs[i].data_ptr();
+    p[size_t(i)].res_out = res_outs.empty() ? nullptr : res_outs[i].data_ptr();
+    p[size_t(i)].workspace = workspaces[i].data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  CollInfo info = fused_gemm_allreduce(c, dtype_of(xs[0]), p.data(), M, N, K, float(eps), with_norm, int(ctas),
+                                       at::cuda::getCurrentCUDAStream(c.device()));
+  return info_vec(info);
+}
+
+int64_t gemm_ar_workspace_bytes(int64_t world, int64_t M, int64_t N) { return int64_t(gemm_ar_workspace(int(world), M, N).total()); }
+
 }  // namespace
 
 TORCH_LIBRARY(b200ipc, m) {
+  m.def(
+      "fused_gemm_ar(Tensor[] xs, Tensor[] ws, Tensor[] residuals, Tensor[] gammas, Tensor[] outs, Tensor[] res_outs, "
+      "Tensor[] workspaces, float eps, bool with_norm, int comm, int ctas) -> int[]",
+      &fused_gemm_ar);
   m.def("all_reduce(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_reduce);
   m.def("all_gather(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_gather);
   m.def("reduce_scatter(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int flags) -> int[]", &reduce_scatter);
@@ -315,6 +361,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                 int64_t(l.half_bytes),   int64_t(l.oneshot_off),  int64_t(l.oneshot_bytes),
                                 int64_t(l.staging_off),  int64_t(l.staging_bytes), int64_t(l.total_bytes)};
   });
+  m.def("gemm_ar_workspace_bytes", &gemm_ar_workspace_bytes);
   m.def("algo_names", &algo_names_help);
   // Parses an algorithm name: (known, is_allgather, automatic, schedule, proto, direct).
   m.def("parse_algo", [](const std::string& name) {

@@ -213,6 +213,38 @@ class Communicator:
         self.last_info = CollInfo.from_vec(v)
         return self._ret(x, outs)
 
+    def linear_allreduce(self, x: TensorOrList, weight: TensorOrList, residual: Optional[TensorOrList] = None,
+                         gamma: Optional[TensorOrList] = None, eps: float = 1e-5, *, ctas: int = 0):
+        """Row-parallel linear layer fused with its all-reduce in one tcgen05/TMA kernel.
+
+        x: [M, K_local], weight: [N, K_local] (nn.Linear layout) of this rank.  Returns
+        `y = all_reduce(x @ weight.T)` when neither residual nor gamma is given, else the pair
+        `(RMSNorm(y + residual) * gamma, y + residual)`.  Outputs live in the symmetric heap and are
+        reused by the next call with the same shape: consume (or copy) them before calling again."""
+        xs = [t.contiguous() for t in self._lists(x)]
+        ws = [t.contiguous() for t in self._lists(weight)]
+        M, N = xs[0].shape[0], ws[0].shape[0]
+        key = (M, N, xs[0].dtype)
+        cache = self.__dict__.setdefault("_gemm_buffers", {})
+        if key not in cache:
+            nbytes = self._C.gemm_ar_workspace_bytes(self.world, M, N)
+            wsp = self.empty([nbytes // 2], torch.float16)
+            for t in (wsp if self._virtual else [wsp]):
+                t.zero_()
+            torch.cuda.synchronize()
+            self.barrier()  # nobody may push into a workspace that its owner is still clearing
+            cache[key] = (wsp, self.empty([M, N], xs[0].dtype), self.empty([M, N], xs[0].dtype))
+        wsp, out, res_out = cache[key]
+        L = (lambda t: t) if self._virtual else (lambda t: [t])
+        with_norm = gamma is not None
+        want_res = residual is not None
+        v = torch.ops.b200ipc.fused_gemm_ar(xs, ws, self._lists(residual) if want_res else [], self._lists(gamma) if with_norm else [],
+                                            L(out), L(res_out) if want_res else [], L(wsp), eps, with_norm, self._h, ctas)
+        self.last_info = CollInfo.from_vec(v)
+        if with_norm or want_res:
+            return out, res_out
+        return out
+
     # ------------------------------------------------------------------ symmetric memory
     def empty(self, shape, dtype=torch.float16):
         """A tensor inside the symmetric heap (same offset on every rank): the large-message

@@ -1,0 +1,65 @@
+"""The tcgen05/TMA row-parallel GEMM fused with its all-reduce (and residual + RMSNorm), against a
+plain PyTorch fp32 reference.  World sizes above one are emulated on the single GPU (one cooperative
+launch, block rows are ranks), which exercises the peer stores, flags and the delivery counter."""
+import pytest
+import torch
+
+from gpu_ipc_example_b200 import Communicator
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(world, M, K, N, dtype, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    xs = [torch.randn(M, K, device="cuda", generator=g).to(dtype) for _ in range(world)]
+    ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.02).to(dtype) for _ in range(world)]
+    res = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    gam = (torch.rand(N, device="cuda", generator=g) + 0.5).to(dtype)
+    return xs, ws, res, gam
+
+
+def _ref(xs, ws):
+    dtype = xs[0].dtype
+    # every rank's partial product is rounded to the element type before the sum, as the kernel does
+    return torch.stack([(x.float() @ w.float().t()).to(dtype).float() for x, w in zip(xs, ws)]).sum(0)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_gemm_allreduce_plain(world):
+    with Communicator.virtual(world, 0, staging_bytes=96 << 20) as comm:
+        for (M, K, N) in ((128, 256, 256), (1, 512, 1024), (16, 448, 512), (300, 512, 1024), (2048, 448, 1024)):
+            xs, ws, _, _ = _mk(world, M, K, N, torch.float16, seed=M)
+            outs = comm.linear_allreduce(xs, ws)
+            torch.cuda.synchronize()
+            comm.check()
+            want = _ref(xs, ws)
+            for o in outs:
+                torch.testing.assert_close(o.float(), want, atol=3e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("world", [1, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gemm_allreduce_residual_rmsnorm(world, dtype):
+    with Communicator.virtual(world, 0, staging_bytes=96 << 20) as comm:
+        for (M, K, N) in ((1, 448, 8192), (16, 448, 8192), (128, 448, 8192), (200, 256, 1024)):
+            xs, ws, res, gam = _mk(world, M, K, N, dtype, seed=7 + M)
+            out, new_res = comm.linear_allreduce(xs, ws, [res] * world, [gam] * world, 1e-5)
+            torch.cuda.synchronize()
+            comm.check()
+            s = (_ref(xs, ws) + res.float()).to(dtype).float()
+            want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float()
+            tol = dict(atol=4e-2, rtol=2e-2) if dtype == torch.float16 else dict(atol=2.5e-1, rtol=5e-2)
+            for o, r in zip(out, new_res):
+                torch.testing.assert_close(r.float(), s, **tol)
+                torch.testing.assert_close(o.float(), want, **tol)
+
+
+def test_repeated_calls_reuse_the_workspace():
+    with Communicator.virtual(4, 0, staging_bytes=64 << 20) as comm:
+        for it in range(6):
+            xs, ws, res, gam = _mk(4, 64, 256, 512, torch.float16, seed=it)
+            out, new_res = comm.linear_allreduce(xs, ws, [res] * 4, [gam] * 4)
+            torch.cuda.synchronize()
+            comm.check()
+            s = (_ref(xs, ws) + res.float()).half().float()
+            torch.testing.assert_close(new_res[3].float(), s, atol=4e-2, rtol=2e-2)
