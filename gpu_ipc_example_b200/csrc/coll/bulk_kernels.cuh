@@ -70,7 +70,8 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapL
   const size_t pad_off = lay.ctrl_off + kCtrlBarrierOff + size_t(blockIdx.x) * kMaxRanks * sizeof(uint32_t);
   if (tid < me.world && tid != me.rank) {
     uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
-    __threadfence_system();
+    // st.release.sys is the only fence: it orders the CTA's earlier accesses (made visible to this
+    // thread by the barrier above) before the signal
     if (!(me.flags & kMuteSends)) {
       st_release_sys_u32(reinterpret_cast<uint32_t*>(me.peer[tid] + pad_off) + me.rank, value);
     }

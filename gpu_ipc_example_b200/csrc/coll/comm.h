@@ -123,6 +123,7 @@ class Comm {
   // (host barrier) in a multi-process world.
   void reset();
   uint32_t seq() const { return seq_; }
+  bool device_seq() const { return device_seq_; }
   void set_seq(uint32_t s) { seq_ = s; }
   uint64_t launches() const { return launches_; }
   void set_timeout_ms(uint64_t ms) { timeout_ns_ = ms * 1000000ull; }

@@ -1,5 +1,9 @@
 #include <algorithm>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <set>
+#include <tuple>
 
 #include "../common/check.h"
 #include "../common/cu_driver.h"
@@ -9,7 +13,8 @@
 namespace b200ipc {
 namespace {
 
-constexpr int kStages128 = 6;  // 6 x (16 KiB + 16 KiB) = 192 KiB of the 227 KiB a CTA may use
+constexpr int kStages256 = 4;  // 4 x (16 KiB + 32 KiB) = 192 KiB of the 227 KiB a CTA may use
+constexpr int kStages128 = 6;  // 6 x (16 KiB + 16 KiB) = 192 KiB
 constexpr int kStages64 = 8;   // 8 x (16 KiB +  8 KiB) = 192 KiB
 
 template <typename T, int BN, int STAGES>
@@ -17,7 +22,23 @@ const void* kernel_ptr() {
   return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES>);
 }
 
+// Tensor maps depend only on (pointer, extents, box, type): weights and activation buffers are
+// reused call after call, so encoding is done once per distinct operand.
+using MapKey = std::tuple<const void*, uint64_t, uint64_t, uint32_t, int>;
+std::mutex g_map_mu;
+std::map<MapKey, CUtensorMap> g_maps;
+std::set<const void*> g_attr_done;
+
 void encode_2d(CUtensorMap* map, DType t, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const MapKey key(base, rows, cols, box_rows, int(t));
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *map = it->second;
+      return;
+    }
+  }
   B200_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "GEMM operands must be 16-byte aligned");
   B200_REQUIRE((cols * 2) % 16 == 0, "the K extent must be a multiple of 8 elements");
   cuuint64_t dims[2] = {cols, rows};
@@ -28,6 +49,9 @@ void encode_2d(CUtensorMap* map, DType t, const void* base, uint64_t rows, uint6
                                           2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = *map;
 }
 
 }  // namespace
@@ -51,17 +75,29 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   B200_REQUIRE(K % 8 == 0, "K must be a multiple of 8");
   B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
-  const bool small_m = M <= 128 || N % 128 != 0;
-  const int BN = small_m ? 64 : 128;
+  // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
+  // cut the operand traffic per FLOP for large M.
+  const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
   const void* fn;
   size_t smem;
-  if (t == DType::F16) {
-    fn = small_m ? kernel_ptr<__half, 64, kStages64>() : kernel_ptr<__half, 128, kStages128>();
+  const bool h = t == DType::F16;
+  if (BN == 64) {
+    fn = h ? kernel_ptr<__half, 64, kStages64>() : kernel_ptr<__nv_bfloat16, 64, kStages64>();
+    smem = sizeof(GemmSmem<64, kStages64>) + 1024;
+  } else if (BN == 128) {
+    fn = h ? kernel_ptr<__half, 128, kStages128>() : kernel_ptr<__nv_bfloat16, 128, kStages128>();
+    smem = sizeof(GemmSmem<128, kStages128>) + 1024;
   } else {
-    fn = small_m ? kernel_ptr<__nv_bfloat16, 64, kStages64>() : kernel_ptr<__nv_bfloat16, 128, kStages128>();
+    fn = h ? kernel_ptr<__half, 256, kStages256>() : kernel_ptr<__nv_bfloat16, 256, kStages256>();
+    smem = sizeof(GemmSmem<256, kStages256>) + 1024;
   }
-  smem = (small_m ? sizeof(GemmSmem<64, kStages64>) : sizeof(GemmSmem<128, kStages128>)) + 1024;
-  B200_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (!g_attr_done.count(fn)) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+      g_attr_done.insert(fn);
+    }
+  }
 
   const int64_t rpr = (M + W - 1) / W;
   const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
@@ -72,8 +108,14 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, std::max<int64_t>(total_tiles, std::min<int64_t>(rpr, cap))));
   B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs, only " << cap << " can run at once");
 
+  int a_box = kGemmBM;
+  if (M < kGemmBM) {
+    a_box = 8;
+    while (a_box < M) a_box *= 2;
+  }
   GemmArArgs args;
   std::memset(&args, 0, sizeof(args));
+  args.a_box_rows = a_box;
   std::vector<const void*> ins(size_t(comm.nlocal()), nullptr);
   std::vector<void*> outs(size_t(comm.nlocal()), nullptr);
   comm.fill_views(&args.k, ins.data(), outs.data(), size_t(M * N), 0);
@@ -94,7 +136,7 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
     B200_REQUIRE(lo == landing_off && oo == out_off && ro == res_off, "symmetric tensors must sit at the same offset on every rank");
     B200_REQUIRE(lo % 256 == 0 && oo % 16 == 0 && ro % 16 == 0, "symmetric tensors must be 16-byte aligned");
     if (with_norm) B200_REQUIRE(p.gamma != nullptr, "RMSNorm needs gamma");
-    encode_2d(&args.tma_a[i], t, p.x, uint64_t(M), uint64_t(K), kGemmBM);
+    encode_2d(&args.tma_a[i], t, p.x, uint64_t(M), uint64_t(K), uint32_t(a_box));
     encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(BN));
     args.residual[i] = p.residual;
     args.gamma[i] = p.gamma;
@@ -110,8 +152,12 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   args.out_off = out_off;
   args.res_out_off = res_off;
   const uint32_t first = comm.take_seq(2);
-  args.done_target = comm.take_done(uint32_t(W) * uint32_t(ctas));
-  for (int i = 0; i < comm.nlocal(); ++i) args.k.v[i].seq = first;
+  const uint32_t deliveries = uint32_t(W) * uint32_t(ctas);
+  args.done_target = comm.device_seq() ? deliveries : comm.take_done(deliveries);
+  for (int i = 0; i < comm.nlocal(); ++i) {
+    args.k.v[i].seq = first;
+    args.k.v[i].seq_step = 2;
+  }
 
   void* params[] = {&args};
   comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);

@@ -33,7 +33,8 @@ namespace b200ipc {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;        // 64 x 2 B = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kGemmThreads = 384;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue; warps 6-11 only
+                                   // join the memory-bound owner phase, which wants many loads in flight
 constexpr uint32_t kMbarSpinLimit = 1u << 24;
 
 struct GemmArArgs {
@@ -44,6 +45,8 @@ struct GemmArArgs {
   const void* gamma[kMaxRanks];              // [N] or nullptr
   int M, N, K;
   int rows_per_rank;
+  int a_box_rows;        // rows of X one TMA box brings in: 128, or fewer when M is small (the rest of the
+                         // 128-row operand tile then holds stale data, which only reaches accumulator rows >= M)
   uint32_t done_target;  // value the local delivery counter reaches when all owners are done
   float eps;
   int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
@@ -153,6 +156,16 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Phase time stamps of CTA 0 (global timer, ns), kept in the control region of the heap at
+// kGemmTraceOff: [0] entry, [1] set-up done, [2] last TMA issued, [3] last MMA committed,
+// [4] last epilogue tile stored, [5] tensor memory returned, [6] owner rows reduced and pushed,
+// [7] exit.  A debugging and tuning aid; costs a handful of timer reads by single threads.
+constexpr size_t kGemmTraceOff = 1024;
+__device__ __forceinline__ void gemm_trace(const RankView& me, const HeapLayout& lay, int slot) {
+  if (blockIdx.x == 0)
+    reinterpret_cast<unsigned long long*>(me.heap + lay.ctrl_off + kGemmTraceOff)[slot] = globaltimer_ns();
+}
+
 template <int BN, int STAGES>
 struct GemmSmem {
   alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
@@ -163,7 +176,170 @@ struct GemmSmem {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float red[8];
+  float red[kGemmThreads / 32];
+};
+
+// The owner's work on one of its rows, shared by the warp-per-row and CTA-per-row forms.  `tid` /
+// `nthr` describe the group of threads that shares the row; a thread touches the same vectors in
+// both passes, so no barrier is needed between them.
+template <typename T>
+struct RowCtx {
+  const RankView* me;
+  const HeapLayout* lay;
+  const GemmArArgs* args;
+  int slot;  // which of the launch's ranks this block row is
+  uint32_t seq;
+  int m_tiles, n_tiles;
+  int* fail;  // shared-memory flag of the CTA
+
+  // Bounded wait until every source rank has delivered every column tile of this row's 32-row group.
+  __device__ bool wait_row_flags(int row, int tid, int nthr) const {
+    const int W = me->world;
+    const int mt = row / kGemmBM;
+    const int grp = (row % kGemmBM) / 32;
+    uint32_t* abort_word = reinterpret_cast<uint32_t*>(me->heap + lay->ctrl_off + kCtrlAbortOff);
+    bool ok = true;
+    for (int f = tid; f < W * n_tiles && ok; f += nthr) {
+      const int src = f / n_tiles, nt = f % n_tiles;
+      const uint32_t* fp = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off) +
+                           ((size_t(src) * m_tiles + mt) * n_tiles + nt) * 4 + grp;
+      uint32_t spins = 0;
+      uint64_t t0 = 0;
+      for (;;) {
+        const uint32_t seen = ld_acquire_sys_u32(fp);
+        if (seen == seq) break;
+        if ((++spins & 0x3fu) == 0) {
+          if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
+            *fail = 1;
+            ok = false;
+            break;
+          }
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > me->timeout_ns) {
+            if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+              StatusBlock* sb = me->status;
+              sb->rank = uint32_t(me->rank);
+              sb->peer = uint32_t(src);
+              sb->wire = blockIdx.x;
+              sb->step = uint32_t(nt);
+              sb->expected = seq;
+              sb->seen = seen;
+              sb->where = 21;
+              __threadfence_system();
+              sb->code = kTimeout;
+              __threadfence_system();
+            }
+            for (int q = 0; q < W; ++q)
+              if (q != me->rank) st_volatile_u32(reinterpret_cast<uint32_t*>(me->peer[q] + lay->ctrl_off + kCtrlAbortOff), 1u);
+            *fail = 1;
+            ok = false;
+            break;
+          }
+        }
+      }
+    }
+    return ok;
+  }
+
+  __device__ uint16_t* my_res_row(int row) const {
+    return reinterpret_cast<uint16_t*>(me->heap + (args->res_out_off ? args->res_out_off : args->out_off)) + size_t(row) * args->N;
+  }
+
+  // Sum of the world partial copies in rank order (+ residual), rounded and kept locally; returns
+  // this thread's share of the sum of squares.
+  __device__ float pass1(int i, int row, int tid, int nthr) const {
+    constexpr int U = 4;
+    const int W = me->world, N = args->N, rpr = args->rows_per_rank;
+    const int nvec = N / 8;
+    const uint16_t* residual = static_cast<const uint16_t*>(args->residual[slot]);
+    uint16_t* my_res = my_res_row(row);
+    float ss = 0.f;
+    for (int v0 = tid; v0 < nvec; v0 += U * nthr) {
+      float a[U][8];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[u][e] = 0.f;
+      for (int src = 0; src < W; ++src) {
+        const char* base = me->heap + args->landing_off + ((size_t(src) * rpr + i) * size_t(N)) * 2;
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * nthr;
+          x[u] = v < nvec ? *reinterpret_cast<const uint4*>(base + size_t(v) * 16) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) acc8_add<T>(a[u], x[u]);
+      }
+      if (residual) {
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + u * nthr;
+          x[u] = v < nvec ? *reinterpret_cast<const uint4*>(residual + size_t(row) * N + size_t(v) * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) acc8_add<T>(a[u], x[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * nthr;
+        if (v >= nvec) continue;
+        const uint4 o = acc8_pack<T>(a[u]);
+        *reinterpret_cast<uint4*>(my_res + size_t(v) * 8) = o;
+        float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        acc8_add<T>(b, o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += b[e] * b[e];
+      }
+    }
+    return ss;
+  }
+
+  // Normalise (if asked) and push the row to every rank.
+  __device__ void pass2(int row, int tid, int nthr, float inv) const {
+    constexpr int U = 4;
+    const int W = me->world, N = args->N;
+    const int nvec = N / 8;
+    const int rank = me->rank;
+    const uint16_t* my_res = my_res_row(row);
+    const uint4* gamma = static_cast<const uint4*>(args->gamma[slot]);
+    const bool mute = (me->flags & kMuteSends) != 0;
+    for (int v0 = tid; v0 < nvec; v0 += U * nthr) {
+      uint4 x[U], g[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * nthr;
+        x[u] = v < nvec ? *reinterpret_cast<const uint4*>(my_res + size_t(v) * 8) : make_uint4(0, 0, 0, 0);
+        g[u] = (args->with_norm && v < nvec) ? gamma[v] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * nthr;
+        if (v >= nvec || mute) continue;
+        uint4 y = x[u];
+        if (args->with_norm) {
+          const uint32_t xs[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+          const uint32_t gs[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+          uint32_t ys[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 xf = Cvt<T>::up(xs[e]);
+            const float2 gf = Cvt<T>::up(gs[e]);
+            ys[e] = Cvt<T>::down(xf.x * inv * gf.x, xf.y * inv * gf.y);
+          }
+          y = make_uint4(ys[0], ys[1], ys[2], ys[3]);
+        }
+        for (int k = 0; k < W; ++k) {
+          const int q = (rank + k) % W;
+          *reinterpret_cast<uint4*>(me->peer[q] + args->out_off + (size_t(row) * N + size_t(v) * 8) * 2) = y;
+          if (args->res_out_off && q != rank)
+            *reinterpret_cast<uint4*>(me->peer[q] + args->res_out_off + (size_t(row) * N + size_t(v) * 8) * 2) = x[u];
+        }
+      }
+    }
+  }
 };
 
 template <typename T, int BN, int STAGES>
@@ -185,11 +361,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   const int k_iters = (K + kGemmBK - 1) / kGemmBK;
   const int total_tiles = m_tiles * n_tiles;
   const int rpr = args.rows_per_rank;
+  // Graph-captured launches: the running flag value and delivery total live on the device and
+  // args.done_target then holds this launch's increment instead of an absolute value.
   uint32_t seq = me.seq;
+  uint32_t done_target = args.done_target;
+  if (me.seq_dev) {
+    seq += ld_volatile_u32(me.seq_dev);
+    done_target += ld_volatile_u32(me.seq_dev + 3);
+  }
   constexpr uint32_t kTmemCols = 2 * BN;
-  constexpr uint32_t kStageBytes = (kGemmBM + BN) * kGemmBK * 2;
+  const uint32_t stage_bytes = uint32_t(args.a_box_rows + BN) * kGemmBK * 2;
 
   // ---- set-up ---------------------------------------------------------------------------
+  if (threadIdx.x == 0) gemm_trace(me, lay, 0);
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&s.full[i], 1);
@@ -211,6 +395,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
+  if (threadIdx.x == 0) gemm_trace(me, lay, 1);
 
   // ---- phase 1: GEMM + reduce-scatter epilogue ---------------------------------------------
   if (warp == 0) {
@@ -224,11 +409,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           const int st = int(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag)) break;
-          mbar_expect_tx(&s.full[st], kStageBytes);
+          mbar_expect_tx(&s.full[st], stage_bytes);
           tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
           tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
         }
       }
+      gemm_trace(me, lay, 2);
       // copies in flight land in this CTA's shared memory: wait for the ones still pending
       for (uint32_t back = 0; back < uint32_t(STAGES) && back < it; ++back) {
         const uint32_t j = it - 1 - back;
@@ -263,8 +449,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
         if (!ok) break;
         umma_commit(&s.acc_full[buf]);  // accumulator complete
       }
+      gemm_trace(me, lay, 3);
     }
-  } else {
+  } else if (warp < 6) {
     // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int lane_group = warp & 3;
     const int row_in_tile = lane_group * 32 + lane;
@@ -312,7 +499,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
         if (last_row > M - 1) last_row = M - 1;
         const int q = first_row / rpr + lane;
         if (q <= last_row / rpr) {
-          __threadfence_system();
+          // st.release.sys orders this warp's row stores (made visible to this lane by the
+          // __syncwarp above) before the flag; no separate fence
           uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[q] + args.flags_off) +
                         ((size_t(rank) * m_tiles + mt) * n_tiles + nt) * 4 + lane_group;
           st_release_sys_u32(f, seq);
@@ -321,11 +509,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     }
   }
 
+  if (threadIdx.x == 64) gemm_trace(me, lay, 4);
   // ---- tensor memory goes back before anything waits on a peer ---------------------------------
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) gemm_trace(me, lay, 5);
   if (*abort_flag) {
     if (threadIdx.x == 0) {
       uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
@@ -344,124 +534,60 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   }
 
   // ---- phase 2/3: owner reduce (+ residual, RMSNorm) and all-gather push ------------------------
+  // Many owned rows: one row per warp (six rows in flight per CTA, no block barrier).  Few rows
+  // (decode): one row per CTA so that all threads share the row.
   const int row0 = rank * rpr;
   int nrows = M - row0;
   if (nrows > rpr) nrows = rpr;
   if (nrows < 0) nrows = 0;
-  const int nvec = N / 8;
   const int nthreads = int(blockDim.x);
-  const uint16_t* residual = static_cast<const uint16_t*>(args.residual[blockIdx.y]);
-  const uint4* gamma = static_cast<const uint4*>(args.gamma[blockIdx.y]);
-  uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
+  const int nwarps = nthreads >> 5;
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
-
-  for (int i = int(blockIdx.x); i < nrows; i += G) {
-    const int row = row0 + i;
-    const int mt = row / kGemmBM;
-    // wait for every source's partial tiles of this row (flags live in my own memory)
-    for (int f = int(threadIdx.x); f < W * n_tiles; f += nthreads) {
-      const int src = f / n_tiles, nt = f % n_tiles;
-      const uint32_t* fp = reinterpret_cast<const uint32_t*>(me.heap + args.flags_off) +
-                           ((size_t(src) * m_tiles + mt) * n_tiles + nt) * 4 + (row % kGemmBM) / 32;
-      uint32_t spins = 0;
-      uint64_t t0 = 0;
-      for (;;) {
-        const uint32_t seen = ld_acquire_sys_u32(fp);
-        if (seen == seq) break;
-        if ((++spins & 0x3fu) == 0) {
-          if (ld_volatile_u32(abort_word) != 0 || s_fail) { s_fail = 1; break; }
-          const uint64_t now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > me.timeout_ns) {
-            if (atomicCAS(abort_word, 0u, 1u) == 0u) {
-              StatusBlock* sb = me.status;
-              sb->rank = uint32_t(rank);
-              sb->peer = uint32_t(src);
-              sb->wire = blockIdx.x;
-              sb->step = uint32_t(nt);
-              sb->expected = seq;
-              sb->seen = seen;
-              sb->where = 21;
-              __threadfence_system();
-              sb->code = kTimeout;
-              __threadfence_system();
-            }
-            for (int q = 0; q < W; ++q)
-              if (q != rank) st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[q] + lay.ctrl_off + kCtrlAbortOff), 1u);
-            s_fail = 1;
-            break;
-          }
-        }
-      }
-    }
-    __syncthreads();
-    if (s_fail) break;
-
-    // pass 1: sum the world copies in rank order (+ residual), keep the rounded row locally
-    uint16_t* my_res = reinterpret_cast<uint16_t*>(me.heap + (args.res_out_off ? args.res_out_off : args.out_off)) + size_t(row) * N;
-    float ss = 0.f;
-    for (int v = int(threadIdx.x); v < nvec; v += nthreads) {
-      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int src = 0; src < W; ++src) {
-        const uint4 x = *reinterpret_cast<const uint4*>(me.heap + args.landing_off + ((size_t(src) * rpr + i) * size_t(N)) * 2 + size_t(v) * 16);
-        acc8_add<T>(a, x);
-      }
-      if (residual) acc8_add<T>(a, *reinterpret_cast<const uint4*>(residual + size_t(row) * N + size_t(v) * 8));
-      const uint4 o = acc8_pack<T>(a);
-      *reinterpret_cast<uint4*>(my_res + size_t(v) * 8) = o;
-      if (args.with_norm) {
-        float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        acc8_add<T>(b, o);
+  RowCtx<T> rc;
+  rc.me = &me;
+  rc.lay = &lay;
+  rc.args = &args;
+  rc.slot = int(blockIdx.y);
+  rc.seq = seq;
+  rc.m_tiles = m_tiles;
+  rc.n_tiles = n_tiles;
+  rc.fail = &s_fail;
+  if (nrows >= 2 * G * nwarps) {
+    for (int i = int(blockIdx.x) * nwarps + warp; i < nrows; i += G * nwarps) {
+      // the verdict must be the same for the whole warp: the shuffles below need every lane
+      if (!__all_sync(0xffffffffu, rc.wait_row_flags(row0 + i, lane, 32))) break;
+      float ss = rc.pass1(i, row0 + i, lane, 32);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += b[e] * b[e];
-      }
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      rc.pass2(row0 + i, lane, 32, rsqrtf(ss / float(N) + args.eps));
     }
-    float inv = 1.f;
-    if (args.with_norm) {
+  } else {
+    for (int i = int(blockIdx.x); i < nrows; i += G) {
+      const bool ok = rc.wait_row_flags(row0 + i, int(threadIdx.x), nthreads);
+      (void)ok;
+      __syncthreads();
+      if (s_fail) break;
+      float ss = rc.pass1(i, row0 + i, int(threadIdx.x), nthreads);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (lane == 0) s.red[warp] = ss;
       __syncthreads();
       float tot = 0.f;
-      for (int w = 0; w < nthreads / 32; ++w) tot += s.red[w];
-      inv = rsqrtf(tot / float(N) + args.eps);
-    }
-    __syncthreads();  // my_res written by all threads; s.red consumed
-    // pass 2: normalise and push both rows to every rank
-    for (int v = int(threadIdx.x); v < nvec; v += nthreads) {
-      const uint4 x = *reinterpret_cast<const uint4*>(my_res + size_t(v) * 8);
-      uint4 y = x;
-      if (args.with_norm) {
-        const uint4 g = gamma[v];
-        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-        const uint32_t gs[4] = {g.x, g.y, g.z, g.w};
-        uint32_t ys[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 xf = Cvt<T>::up(xs[e]);
-          const float2 gf = Cvt<T>::up(gs[e]);
-          ys[e] = Cvt<T>::down(xf.x * inv * gf.x, xf.y * inv * gf.y);
-        }
-        y = make_uint4(ys[0], ys[1], ys[2], ys[3]);
-      }
-      if (!(me.flags & kMuteSends)) {
-        for (int k = 0; k < W; ++k) {
-          const int q = (rank + k) % W;
-          *reinterpret_cast<uint4*>(me.peer[q] + args.out_off + (size_t(row) * N + size_t(v) * 8) * 2) = y;
-          if (args.res_out_off && q != rank)
-            *reinterpret_cast<uint4*>(me.peer[q] + args.res_out_off + (size_t(row) * N + size_t(v) * 8) * 2) = x;
-        }
-      }
+      for (int w = 0; w < nwarps; ++w) tot += s.red[w];
+      rc.pass2(row0 + i, int(threadIdx.x), nthreads, rsqrtf(tot / float(N) + args.eps));
+      __syncthreads();  // s.red is reused by the next row
     }
   }
 
   // ---- phase 4: tell everyone this CTA has delivered; CTA 0 waits for all deliveries ---------------
   __syncthreads();
+  if (threadIdx.x == 0) gemm_trace(me, lay, 6);
+  uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
   uint32_t* done = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlSeqOff) + 4;
   if (threadIdx.x < uint32_t(W) && !(me.flags & kMuteSends) && !s_fail) {
-    __threadfence_system();
+    // release semantics of the reduction order the CTA's pushes (synchronised by the barrier above) before it
     red_release_sys_add(reinterpret_cast<uint32_t*>(me.peer[threadIdx.x] + lay.ctrl_off + kCtrlSeqOff) + 4, 1u);
   }
   if (blockIdx.x == 0 && threadIdx.x == 0 && !s_fail) {
@@ -469,7 +595,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     uint64_t t0 = 0;
     for (;;) {
       const uint32_t seen = ld_acquire_sys_u32(done);
-      if (int32_t(seen - args.done_target) >= 0) break;
+      if (int32_t(seen - done_target) >= 0) break;
       if ((++spins & 0x3fu) == 0) {
         if (ld_volatile_u32(abort_word) != 0) break;
         const uint64_t now = globaltimer_ns();
@@ -480,7 +606,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
             sb->rank = uint32_t(rank);
             sb->peer = 0;
             sb->wire = 0;
-            sb->expected = args.done_target;
+            sb->expected = done_target;
             sb->seen = seen;
             sb->where = 22;
             __threadfence_system();
@@ -489,6 +615,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           }
           break;
         }
+      }
+    }
+  }
+  if (threadIdx.x == 0) gemm_trace(me, lay, 7);
+  if (me.seq_dev) {
+    // the last CTA to leave advances the device-side flag value and delivery total
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(me.seq_dev + 1, 1u) == gridDim.x - 1) {
+        me.seq_dev[1] = 0;
+        me.seq_dev[0] += me.seq_step;
+        me.seq_dev[3] += args.done_target;
+        __threadfence();
       }
     }
   }

@@ -109,6 +109,44 @@ def mode_collectives(comm, nvls):
 
 
 @soft
+def check_linear(comm, M, K, N, dtype=torch.float16, norm=True):
+    rank = dist.get_rank()
+    g = torch.Generator(device="cuda").manual_seed(300 + rank)
+    x = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).to(dtype)
+    gr = torch.Generator(device="cuda").manual_seed(77)
+    res = torch.randn(M, N, device="cuda", generator=gr).to(dtype)
+    gam = (torch.rand(N, device="cuda", generator=gr) + 0.5).to(dtype)
+    part = (x.float() @ w.float().t()).to(dtype)
+    total = torch.stack([p.float() for p in gather_inputs(part)]).sum(0)
+    if norm:
+        out, new_res = comm.linear_allreduce(x, w, res, gam, 1e-5)
+        torch.cuda.synchronize()
+        comm.check()
+        s = (total + res.float()).to(dtype).float()
+        want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float()
+        torch.testing.assert_close(new_res.float(), s, atol=4e-2, rtol=2e-2)
+        torch.testing.assert_close(out.float(), want, atol=4e-2, rtol=2e-2)
+        outs = gather_inputs(out.clone())
+        for o in outs:
+            assert torch.equal(o, outs[0]), "ranks differ"
+    else:
+        out = comm.linear_allreduce(x, w)
+        torch.cuda.synchronize()
+        comm.check()
+        torch.testing.assert_close(out.float(), total, atol=4e-2, rtol=2e-2)
+
+
+@soft
+def mode_linear(comm):
+    for (M, K, N) in ((1, 448, 8192), (16, 448, 8192), (128, 256, 1024), (300, 512, 1024), (2048, 448, 2048)):
+        check_linear(comm, M, K, N, norm=True)
+        check_linear(comm, M, K, N, norm=False)
+    for it in range(20):
+        check_linear(comm, 32, 256, 512, norm=True)
+
+
+@soft
 def mode_faults(comm):
     """Rank 1 sends nothing for one collective: every rank's bounded wait ends with a status,
     nobody hangs, and after a collective reset the communicator works again."""
@@ -150,6 +188,8 @@ def main():
         elif mode == "hostmem":
             for algo in ("small", "simple_pcie_p", "oneshot", "simple_ring"):
                 check_allreduce(comm, algo, 14336)
+        elif mode == "linear":
+            mode_linear(comm)
         elif mode == "faults":
             mode_faults(comm)
     except Exception as e:  # noqa: BLE001

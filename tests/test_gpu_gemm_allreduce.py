@@ -63,3 +63,24 @@ def test_repeated_calls_reuse_the_workspace():
             comm.check()
             s = (_ref(xs, ws) + res.float()).half().float()
             torch.testing.assert_close(new_res[3].float(), s, atol=4e-2, rtol=2e-2)
+
+
+def test_graph_replay_with_device_side_counters():
+    with Communicator.virtual(4, 0, staging_bytes=64 << 20, device_seq=True) as comm:
+        xs, ws, res, gam = _mk(4, 32, 256, 512, torch.float16, seed=3)
+        s = (_ref(xs, ws) + res.float()).half().float()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            comm.linear_allreduce(xs, ws, [res] * 4, [gam] * 4)  # allocates the workspace outside the capture
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                out, new_res = comm.linear_allreduce(xs, ws, [res] * 4, [gam] * 4)
+                out, new_res = comm.linear_allreduce(xs, ws, [res] * 4, [gam] * 4)
+            for _ in range(3):
+                for t in new_res:
+                    t.zero_()
+                g.replay()
+                stream.synchronize()
+                comm.check()
+                torch.testing.assert_close(new_res[2].float(), s, atol=4e-2, rtol=2e-2)

@@ -43,6 +43,13 @@ def test_nvls(world):
         pytest.skip("multicast not available on this box: " + out)
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_fused_gemm_allreduce(world):
+    if world not in _worlds():
+        pytest.skip("not enough GPUs")
+    _run("linear", world)
+
+
 def test_host_memory_scratch():
     if 2 not in _worlds():
         pytest.skip("not enough GPUs")
