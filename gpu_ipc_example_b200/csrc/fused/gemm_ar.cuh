@@ -174,6 +174,7 @@ struct GemmSmem {
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  alignas(16) unsigned char epi[4][32 * 128];  // transpose patch of each epilogue warp
   uint32_t tmem_base;
   int abort_flag;
   float red[kGemmThreads / 32];
@@ -454,7 +455,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   } else if (warp < 6) {
     // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int lane_group = warp & 3;
-    const int row_in_tile = lane_group * 32 + lane;
     uint32_t tile_i = 0;
     for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
       const int mt = t / n_tiles, nt = t % n_tiles;
@@ -462,20 +462,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       const uint32_t use = tile_i >> 1;
       if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag)) break;
       tc_fence_after_sync();
-      const int row = mt * kGemmBM + row_in_tile;
-      const int owner = row / rpr;
-      const bool live = row < M && !(me.flags & kMuteSends);
-      // destination: the owner's landing zone, block of this source rank
-      char* dst = nullptr;
-      if (row < M)
-        dst = me.peer[owner] + args.landing_off +
-              ((size_t(rank) * rpr + size_t(row - owner * rpr)) * size_t(N) + size_t(nt) * BN) * 2;
+      // The accumulator comes out of tensor memory one row per lane.  Written like that, a warp
+      // store would be 32 pieces of 16 bytes 2 N bytes apart - poison for NVLink.  So each 64-column
+      // chunk is rounded, transposed through a swizzled 4 KiB shared-memory patch and stored with
+      // eight lanes per row: every store instruction writes four full 128-byte lines.
+      unsigned char* patch = s.epi[lane_group];
+      const bool mute = (me.flags & kMuteSends) != 0;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < BN; c += 64) {
         uint32_t acc[32];
-        tmem_ld_32cols(tmem_base + (uint32_t(lane_group * 32) << 16) + buf * BN + uint32_t(c), acc);
-        tmem_ld_wait();
-        if (live) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          tmem_ld_32cols(tmem_base + (uint32_t(lane_group * 32) << 16) + buf * BN + uint32_t(c + 32 * h), acc);
+          tmem_ld_wait();
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 o;
@@ -483,9 +482,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
             o.y = Cvt<T>::down(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
             o.z = Cvt<T>::down(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
             o.w = Cvt<T>::down(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
-            *reinterpret_cast<uint4*>(dst + (c + 8 * v) * 2) = o;
+            const int chunk = 4 * h + v;  // 16-byte chunk of this lane's 128-byte row
+            *reinterpret_cast<uint4*>(patch + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = o;
           }
         }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int pr = it * 4 + (lane >> 3);  // row of the patch this lane stores
+          const int chunk = lane & 7;
+          const uint4 o = *reinterpret_cast<const uint4*>(patch + pr * 128 + ((chunk ^ (pr & 7)) * 16));
+          const int row = mt * kGemmBM + lane_group * 32 + pr;
+          if (row < M && !mute) {
+            const int owner = row / rpr;
+            char* dst = me.peer[owner] + args.landing_off +
+                        ((size_t(rank) * rpr + size_t(row - owner * rpr)) * size_t(N) + size_t(nt) * BN + size_t(c) + size_t(chunk) * 8) * 2;
+            *reinterpret_cast<uint4*>(dst) = o;
+          }
+        }
+        __syncwarp();  // the patch is rewritten by the next chunk
       }
       // accumulator buffer free again
       tc_fence_before_sync();
