@@ -4,7 +4,7 @@
     python -m torch.distributed.run --nproc-per-node 8 -m gpu_ipc_example_b200.bench_fused_layer
 
 Default shapes are the Llama-3-70B down-projection at TP = 8: K = 3584 per rank, N = 8192,
-M in {1, 16, 128, 2048}; X ~ N(0,1), W ~ N(0,0.02), residual ~ N(0,1), gamma = 1, eps = 1e-5, fp16.
+M in {1, 16, 128, 2048} (`--rows`); X ~ N(0,1), W ~ N(0,0.02), residual ~ N(0,1), gamma = 1, eps = 1e-5, fp16.
 
 Arms (same inputs, 3 rotating weight copies so that small-M cases stream the weight from HBM rather
 than L2).  Every arm is timed twice with CUDA events on the launching stream, max over ranks:
@@ -44,7 +44,7 @@ def load_peaks():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, nargs="*", default=[1, 16, 128, 2048])
+    ap.add_argument("--rows", dest="m", type=int, nargs="*", default=[1, 16, 128, 2048], help="values of M")
     ap.add_argument("--k", type=int, default=3584)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=30)
