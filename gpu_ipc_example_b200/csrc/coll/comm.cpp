@@ -220,6 +220,7 @@ void Comm::reset() {
   seq_ = (seq_ + 0x10000u) | 1u;
   bar_seq_ = 0;
   gemm_done_ = 0;
+  ag_arrive_ = 0;
   host_barrier();
 }
 

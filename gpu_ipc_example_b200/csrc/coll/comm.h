@@ -147,6 +147,17 @@ class Comm {
     gemm_done_ += inc;
     return gemm_done_;
   }
+  // The same for the arrival counters of the all-gather + GEMM kernel; the second value is the
+  // parity of the launch (which of the two gathered-input buffers it uses).
+  uint32_t take_arrivals(uint32_t inc, int* parity) {
+    ag_arrive_ += inc;
+    *parity = int(ag_launches_++ & 1u);
+    return ag_arrive_;
+  }
+  void reset_fused_counters() {
+    gemm_done_ = 0;
+    ag_arrive_ = 0;
+  }
 
  private:
   Comm() = default;
@@ -165,6 +176,8 @@ class Comm {
   uint32_t seq_ = 1;
   uint32_t bar_seq_ = 0;
   uint32_t gemm_done_ = 0;
+  uint32_t ag_arrive_ = 0;
+  uint32_t ag_launches_ = 0;
   bool device_seq_ = false;
   uint64_t timeout_ns_ = 2000000000ull;
   int max_ctas_ = 0;

@@ -48,4 +48,14 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N);
 CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
                               bool with_norm, int ctas, cudaStream_t stream);
 
+// All-gather of row-sharded activations fused with the GEMM that consumes them: see ag_gemm.cuh.
+struct AgGemmPtrs {
+  const void* x_shard;  // [M / world, K] this rank's rows
+  const void* w;        // [N_local, K] this rank's weight slice (nn.Linear layout)
+  void* out;            // [M, N_local]
+  void* workspace;      // 2 * M * K * 2 bytes in the symmetric heap (two gathered-input buffers)
+};
+CollInfo fused_allgather_gemm(Comm& comm, DType t, const AgGemmPtrs* ptrs, int64_t M, int64_t N, int64_t K, int ctas,
+                              cudaStream_t stream);
+
 }  // namespace b200ipc

@@ -8,6 +8,7 @@
 #include "../common/check.h"
 #include "../common/cu_driver.h"
 #include "fused_ops.h"
+#include "ag_gemm.cuh"
 #include "gemm_ar.cuh"
 
 namespace b200ipc {
@@ -170,6 +171,91 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   info.nwires = ctas * kGemmThreads / 32;
   info.steps = (total_tiles + ctas - 1) / ctas;
   info.first_flag = first;
+  info.launches = 1;
+  return info;
+}
+
+namespace {
+template <typename T, int BN, int STAGES>
+const void* ag_kernel_ptr() {
+  return reinterpret_cast<const void*>(&ag_gemm_kernel<T, BN, STAGES>);
+}
+}  // namespace
+
+CollInfo fused_allgather_gemm(Comm& comm, DType t, const AgGemmPtrs* ptrs, int64_t M, int64_t N, int64_t K, int ctas_req,
+                              cudaStream_t stream) {
+  const int W = comm.world();
+  B200_REQUIRE(M > 0 && N > 0 && K > 0, "empty GEMM");
+  B200_REQUIRE(N % 64 == 0 && K % 8 == 0, "N must be a multiple of 64 and K of 8");
+  B200_REQUIRE(M % W == 0, "the rows of X must divide evenly over the ranks");
+  B200_REQUIRE(!comm.device_seq(), "the all-gather + GEMM kernel keeps its counters on the host");
+  B200_CUDA_CHECK(cudaSetDevice(comm.device()));
+  const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  const void* fn;
+  size_t smem;
+  const bool h = t == DType::F16;
+  if (BN == 64) {
+    fn = h ? ag_kernel_ptr<__half, 64, kStages64>() : ag_kernel_ptr<__nv_bfloat16, 64, kStages64>();
+    smem = sizeof(GemmSmem<64, kStages64>) + 1024;
+  } else if (BN == 128) {
+    fn = h ? ag_kernel_ptr<__half, 128, kStages128>() : ag_kernel_ptr<__nv_bfloat16, 128, kStages128>();
+    smem = sizeof(GemmSmem<128, kStages128>) + 1024;
+  } else {
+    fn = h ? ag_kernel_ptr<__half, 256, kStages256>() : ag_kernel_ptr<__nv_bfloat16, 256, kStages256>();
+    smem = sizeof(GemmSmem<256, kStages256>) + 1024;
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (!g_attr_done.count(fn)) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+      g_attr_done.insert(fn);
+    }
+  }
+  const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
+  const int64_t total_tiles = m_tiles * (N / BN);
+  int cap = comm.resident_ctas(reinterpret_cast<KernelFn>(const_cast<void*>(fn)), kGemmThreads, smem);
+  B200_REQUIRE(cap >= 1, "GEMM kernel does not fit on the device");
+  int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, total_tiles));
+  B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs, only " << cap << " can run at once");
+
+  AgGemmArgs args;
+  std::memset(&args, 0, sizeof(args));
+  std::vector<const void*> ins(size_t(comm.nlocal()), nullptr);
+  std::vector<void*> outs(size_t(comm.nlocal()), nullptr);
+  comm.fill_views(&args.k, ins.data(), outs.data(), size_t(M * N), 0);
+  int parity = 0;
+  args.arrive_target = comm.take_arrivals(uint32_t(ctas), &parity);
+  const size_t buf_bytes = (size_t(M) * size_t(K) * 2 + 255) / 256 * 256;
+  size_t ws_off = SIZE_MAX;
+  for (int i = 0; i < comm.nlocal(); ++i) {
+    const AgGemmPtrs& p = ptrs[i];
+    const size_t off = comm.sym_offset_of(p.workspace, i);
+    B200_REQUIRE(off != SIZE_MAX && off % 256 == 0, "the workspace must be a tensor from the symmetric heap (Communicator.empty)");
+    if (i == 0) ws_off = off;
+    B200_REQUIRE(off == ws_off, "the workspace must sit at the same offset on every rank");
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(p.x_shard) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0,
+                 "x and out must be 16-byte aligned");
+    const size_t xfull_off = ws_off + size_t(parity) * buf_bytes;
+    encode_2d(&args.tma_a[i], t, comm.sym_ptr(xfull_off, i), uint64_t(M), uint64_t(K), kGemmBM);
+    encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(BN));
+    args.x_shard[i] = p.x_shard;
+    args.out[i] = p.out;
+    args.xfull_off = xfull_off;
+  }
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  args.rows_per_rank = int(M / W);
+  void* params[] = {&args};
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+  CollInfo info;
+  info.sched = SchedKind::Bulk;
+  info.proto = ProtoKind::LL512;
+  info.ctas = ctas;
+  info.warps = kGemmThreads / 32;
+  info.nwires = ctas * kGemmThreads / 32;
+  info.steps = (total_tiles + ctas - 1) / ctas;
+  info.first_flag = args.arrive_target;
   info.launches = 1;
   return info;
 }

@@ -305,11 +305,37 @@ std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::T
   return info_vec(info);
 }
 
+// All-gather of row-sharded activations + column-parallel linear.  xs: [M / world, K] per rank, ws: [N_local, K],
+// outs: [M, N_local]; workspaces: symmetric tensors of at least 2 * M * K elements.
+std::vector<int64_t> fused_ag_gemm(std::vector<at::Tensor> xs, std::vector<at::Tensor> ws, std::vector<at::Tensor> outs,
+                                   std::vector<at::Tensor> workspaces, int64_t comm_id, int64_t ctas) {
+  Comm& c = get(comm_id);
+  check_tensors(c, xs, "x");
+  check_tensors(c, ws, "weight");
+  check_tensors(c, outs, "output");
+  check_tensors(c, workspaces, "workspace");
+  TORCH_CHECK(xs[0].dim() == 2 && ws[0].dim() == 2, "b200ipc: x must be [M / world, K] and weight [N, K]");
+  const int64_t M = xs[0].size(0) * c.world(), K = xs[0].size(1), N = ws[0].size(0);
+  TORCH_CHECK(ws[0].size(1) == K, "b200ipc: weight must be [N, K] with the same K as x");
+  std::vector<AgGemmPtrs> p(size_t(c.nlocal()));
+  for (int i = 0; i < c.nlocal(); ++i) {
+    TORCH_CHECK(xs[i].sizes() == xs[0].sizes() && ws[i].sizes() == ws[0].sizes() && outs[i].numel() == M * N,
+                "b200ipc: shape mismatch between ranks");
+    TORCH_CHECK(xs[i].scalar_type() == ws[i].scalar_type() && xs[i].scalar_type() == outs[i].scalar_type(), "b200ipc: dtype mismatch");
+    TORCH_CHECK(workspaces[i].numel() * workspaces[i].element_size() >= 2 * (M * K * 2 + 256), "b200ipc: workspace too small");
+    p[size_t(i)] = {xs[i].data_ptr(), ws[i].data_ptr(), outs[i].data_ptr(), workspaces[i].data_ptr()};
+  }
+  c10::cuda::CUDAGuard guard(c.device());
+  CollInfo info = fused_allgather_gemm(c, dtype_of(xs[0]), p.data(), M, N, K, int(ctas), at::cuda::getCurrentCUDAStream(c.device()));
+  return info_vec(info);
+}
+
 int64_t gemm_ar_workspace_bytes(int64_t world, int64_t M, int64_t N) { return int64_t(gemm_ar_workspace(int(world), M, N).total()); }
 
 }  // namespace
 
 TORCH_LIBRARY(b200ipc, m) {
+  m.def("fused_ag_gemm(Tensor[] xs, Tensor[] ws, Tensor[] outs, Tensor[] workspaces, int comm, int ctas) -> int[]", &fused_ag_gemm);
   m.def(
       "fused_gemm_ar(Tensor[] xs, Tensor[] ws, Tensor[] residuals, Tensor[] gammas, Tensor[] outs, Tensor[] res_outs, "
       "Tensor[] workspaces, float eps, bool with_norm, int comm, int ctas) -> int[]",

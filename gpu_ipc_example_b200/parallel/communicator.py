@@ -245,6 +245,27 @@ class Communicator:
             return out, res_out
         return out
 
+    def allgather_linear(self, x_shard: TensorOrList, weight: TensorOrList, *, ctas: int = 0):
+        """Column-parallel linear layer on row-sharded activations, all-gather fused into the GEMM kernel.
+
+        x_shard: [M / world, K] (this rank's rows), weight: [N_local, K].  Returns `concat(x_shards) @ weight.T`,
+        shape [M, N_local]: every rank pushes its rows to all ranks and the tcgen05/TMA GEMM starts on the rows
+        that are already there while the others arrive."""
+        xs = [t.contiguous() for t in self._lists(x_shard)]
+        ws = [t.contiguous() for t in self._lists(weight)]
+        M, K, N = xs[0].shape[0] * self.world, xs[0].shape[1], ws[0].shape[0]
+        cache = self.__dict__.setdefault("_ag_buffers", {})
+        key = (M, K)
+        if key not in cache:
+            cache[key] = self.empty([2 * (M * K + 128)], xs[0].dtype)
+            torch.cuda.synchronize()
+            self.barrier()
+        wsp = cache[key]
+        outs = [torch.empty(M, N, dtype=t.dtype, device=t.device) for t in xs]
+        v = torch.ops.b200ipc.fused_ag_gemm(xs, ws, outs, wsp if self._virtual else [wsp], self._h, ctas)
+        self.last_info = CollInfo.from_vec(v)
+        return self._ret(x_shard, outs)
+
     # ------------------------------------------------------------------ symmetric memory
     def empty(self, shape, dtype=torch.float16):
         """A tensor inside the symmetric heap (same offset on every rank): the large-message

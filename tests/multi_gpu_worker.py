@@ -138,7 +138,23 @@ def check_linear(comm, M, K, N, dtype=torch.float16, norm=True):
 
 
 @soft
+def check_ag_linear(comm, M, K, N):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    g = torch.Generator(device="cuda").manual_seed(900 + rank)
+    shard = torch.randn(M // world, K, device="cuda", generator=g).half()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).half()
+    x = torch.cat(gather_inputs(shard))
+    for _ in range(3):
+        out = comm.allgather_linear(shard, w)
+        torch.cuda.synchronize()
+        comm.check()
+        torch.testing.assert_close(out.float(), x.float() @ w.float().t(), atol=3e-2, rtol=1e-2)
+
+
+@soft
 def mode_linear(comm):
+    for (M, K, N) in ((128, 256, 256), (320, 448, 512), (2048, 512, 1024), (16, 512, 192)):
+        check_ag_linear(comm, M, K, N)
     for (M, K, N) in ((1, 448, 8192), (16, 448, 8192), (128, 256, 1024), (300, 512, 1024), (2048, 448, 2048)):
         check_linear(comm, M, K, N, norm=True)
         check_linear(comm, M, K, N, norm=False)

@@ -84,3 +84,20 @@ def test_graph_replay_with_device_side_counters():
                 stream.synchronize()
                 comm.check()
                 torch.testing.assert_close(new_res[2].float(), s, atol=4e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_allgather_linear(world):
+    """All-gather fused into the GEMM: row-sharded X, column-parallel W, against fp32 matmul."""
+    with Communicator.virtual(world, 0, staging_bytes=96 << 20) as comm:
+        for (M, K, N) in ((128, 256, 256), (8 * 40, 448, 512), (2048, 512, 1024), (16, 512, 192)):
+            g = torch.Generator(device="cuda").manual_seed(M + world)
+            x = torch.randn(M, K, device="cuda", generator=g).half()
+            ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).half() for _ in range(world)]
+            shards = list(x.chunk(world, dim=0))
+            for rep in range(3):  # the gathered-input buffer alternates between two halves
+                outs = comm.allgather_linear([s.contiguous() for s in shards], ws)
+                torch.cuda.synchronize()
+                comm.check()
+                for o, w in zip(outs, ws):
+                    torch.testing.assert_close(o.float(), x.float() @ w.float().t(), atol=3e-2, rtol=1e-2)
