@@ -22,11 +22,10 @@ void fill_pattern(DType t, uint16_t* dst, int rank, size_t n);
 // (all-gather) from a counter-based generator seeded by the rank.
 void fill_random(DType t, uint16_t* dst, int rank, size_t n, bool uniform);
 
-enum class SumOrder { OwnerRotation, RankOrder };
-// Expected all-reduce result of the deterministic pattern or of explicit inputs.
+// Expected all-reduce of explicit inputs, summed in rank order 0..N-1.
 //   round_each=true sums in T like the reference; otherwise fp32 accumulate, one rounding.
-//   OwnerRotation: element in chunk y is summed as y, y+1, ..., (two-phase schedules);
-//   RankOrder: 0, 1, ..., N-1 (one-shot, bulk).
+// (The two-phase schedules add in owner rotation y, y+1, ...; for the integer pattern every order
+// gives the same bits, for random data the comparison uses a tolerance.)
 void cpu_all_reduce(DType t, const std::vector<const uint16_t*>& inputs, uint16_t* result, size_t n, bool round_each);
 void cpu_all_gather(const std::vector<const uint16_t*>& inputs, uint16_t* result, size_t n_per_rank);
 
