@@ -94,7 +94,7 @@ void usage() {
       "      --ref-accum     round to the element type after every add, like the reference\n"
       "      --random        N(0,1) / U(-1,1) data instead of the (i%%32)*(rank+1) pattern\n"
       "      --sweep LO:HI   time 2^LO .. 2^HI elements\n"
-      "      --timeout-ms T  budget of one device-side wait (default 2000)\n"
+      "      --timeout-ms T  time limit of one device-side wait (default 2000)\n"
       "      --staging-mb M  staging region of the heap (default 256)\n"
       "      --backing B     auto | vmm-fd | cuda-ipc | host-shm\n"
       "      --symmetric     buffers inside the symmetric heap (zero-copy for bulk / nvls)\n"

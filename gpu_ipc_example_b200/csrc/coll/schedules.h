@@ -26,7 +26,7 @@
 //   B::acc_to_msg(Msg&, const Acc&)
 // and a context Cx with the rank's pointers plus
 //   bool Cx::wait(Msg&, const char* src, uint32 flag, int site, int peer, int step)
-// which spins on try_recv under a time budget and returns false when the
+// which spins on try_recv under a time limit and returns false when the
 // collective has been aborted (the wire then returns at once).
 //
 // Capability parity (schedules): parallel_transmit.hpp:62-132 (two-phase,

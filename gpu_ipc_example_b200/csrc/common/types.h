@@ -102,7 +102,7 @@ struct RankView {
   void* out;
   uint64_t nelems;
   StatusBlock* status;     // pinned host memory
-  uint64_t timeout_ns;     // budget of one bounded wait
+  uint64_t timeout_ns;     // time limit of one bounded wait
   uint32_t bar_seq;        // barrier generation for Bulk/Nvls
   uint32_t seq_step;       // how far this launch advances the device-side sequence counter
   uint32_t* seq_dev;       // {offset, done-counter} in device memory when launches are graph-captured, else nullptr

@@ -8,7 +8,7 @@
 // (the reference adds in half/bf16, rt64_128.hpp:950-966).
 //
 // Bounded waits: a spin checks the abort word and the global timer every 256
-// polls; the first wire that runs out of budget records where it was, raises
+// polls; the first wire that runs out of time records where it was, raises
 // the abort word on every rank it can reach and returns, so a missing peer
 // ends the kernel with a status instead of hanging the GPU.
 #pragma once

@@ -214,7 +214,7 @@ def test_fused_allreduce_scale_cast(comm):
 
 
 def test_bounded_wait_reports_instead_of_hanging():
-    """A rank that sends nothing: the others' waits run out (50 ms budget), the kernel returns,
+    """A rank that sends nothing: the others' waits run out (50 ms limit), the kernel returns,
     the status block says who was waited for, and after reset() the communicator works again."""
     c = Communicator.virtual(2, 0, staging_bytes=8 << 20, timeout_ms=50)
     try:
