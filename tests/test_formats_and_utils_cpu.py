@@ -53,3 +53,18 @@ def test_bandwidth_conventions():
     big = utils.fused_layer_roofline_seconds(2048, 3584, 8192, 8, p)
     assert big == pytest.approx(2 * 7 / 8 * 2048 * 8192 * 2 / 770e9)
     assert utils.fused_layer_roofline_seconds(1, 3584, 8192, 1, p) == pytest.approx(2 * 3584 * 8192 / 1590e12)
+
+
+def test_tuner_picks_the_fastest_algorithm_per_size():
+    from gpu_ipc_example_b200 import tune
+
+    a = tune.parse_sweep("# world 8\n#  elements bytes ctas warps time_us(max) algbw busbw\n"
+                         "  1024 2048 1 8 10.00 0.2 0.4\n  1048576 2097152 64 16 60.00 30.0 60.0\n")
+    b = tune.parse_sweep("  1024 2048 1 8 12.00 0.2 0.3\n  1048576 2097152 64 16 23.00 90.0 150.0\n  4194304 8388608 64 16 40.0 200 350\n")
+    assert a == {1024: 10.0, 1048576: 60.0}
+    rows = tune.best_per_size({"oneshot:ll512": a, "parallel:ll512": b})
+    assert [(r[0], r[1]) for r in rows] == [(1024, "oneshot:ll512"), (1048576, "parallel:ll512"), (4194304, "parallel:ll512")]
+    merged = tune.merge_rows(rows)
+    assert merged == [(2048, "oneshot:ll512"), (0, "parallel:ll512")]
+    cpp = tune.as_cpp(merged)
+    assert "{2 * KiB, SchedKind::OneShot, ProtoKind::LL512}," in cpp and "{0, SchedKind::Parallel, ProtoKind::LL512}," in cpp
