@@ -178,8 +178,12 @@ int run_rank(int rank, int world, const Options& opt, UnixMesh* mesh) {
   AlgoSpec algo;
   bool is_ag = false;
   if (!parse_algo(opt.algo, &algo, &is_ag)) {
-    std::fprintf(stderr, "unknown algorithm '%s'\nknown: %s\n", opt.algo.c_str(), algo_names_help().c_str());
-    return 2;
+    // with --baseline nccl the -a value only says which collective: anything naming "allgather" is one
+    if (opt.baseline.empty()) {
+      std::fprintf(stderr, "unknown algorithm '%s'\nknown: %s\n", opt.algo.c_str(), algo_names_help().c_str());
+      return 2;
+    }
+    is_ag = opt.algo.find("allgather") != std::string::npos;
   }
   B200_REQUIRE(opt.simd == 32, "-s " << opt.simd << ": a wire is one warp of 32 lanes on this hardware");
   const DType dt = (opt.dtype == "bf16" || opt.dtype == "bfloat16") ? DType::BF16 : DType::F16;
