@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -136,7 +137,31 @@ def main():
     sys.stdout.flush()
     json_out = os.fdopen(os.dup(1), "w")
     os.dup2(2, 1)
+    state = {"comm": None, "stage": "start"}
+    try:
+        return run(args, json_out, state)
+    except BaseException as e:  # noqa: BLE001 - a benchmark that dies must say where and why
+        import traceback
 
+        rank = int(os.environ.get("RANK", 0))
+        status = None
+        try:
+            if state["comm"] is not None:
+                status = state["comm"].status()
+        except Exception:  # noqa: BLE001
+            pass
+        err = {"error": f"{type(e).__name__}: {e}"[:2000], "stage": state["stage"], "rank": rank, "status": status,
+               "impl": args.impl, "n_gpus": args.gpus}
+        sys.stderr.write(f"[bench rank {rank}] FAILED at stage '{state['stage']}': {err['error']}\nstatus: {status}\n")
+        traceback.print_exc(file=sys.stderr)
+        sys.stderr.flush()
+        json_out.write(json.dumps(err) + "\n")
+        json_out.flush()
+        # the other ranks may be waiting on this one inside a collective: leave without the common teardown
+        os._exit(1)
+
+
+def run(args, json_out, state):
     import torch
     import torch.distributed as dist
 
@@ -159,15 +184,17 @@ def main():
 
     emu_world = args.virtual_world if not multi else world
     comm = None
+    state["stage"] = "communicator"
     if args.impl == "ours":
         staging = nbuf * nbytes + (64 << 20) + (0 if args.no_sweep else (2 << 26) * 2 * 2 + (64 << 20))
         if multi:
             comm = Communicator.from_torch_distributed(local, staging_bytes=staging, nvls=not args.no_nvls)
         else:
             comm = Communicator.virtual(emu_world, local, staging_bytes=staging)
+        state["comm"] = comm
 
-    def make_bufs():
-        if args.impl == "ours":
+    def make_bufs(symmetric):
+        if symmetric:
             bufs = [comm.empty([n], torch.float16) for _ in range(nbuf)]  # symmetric: no staging copy
         else:
             bufs = [torch.empty(n, dtype=torch.float16, device="cuda") for _ in range(nbuf)]
@@ -177,7 +204,8 @@ def main():
                 t.copy_((torch.randn(n, device="cuda", generator=g) * 1e-3).half())
         return bufs
 
-    bufs = make_bufs()
+    state["stage"] = "buffers"
+    bufs = make_bufs(args.impl == "ours")
 
     def step(i):
         b = bufs[i % nbuf]
@@ -211,29 +239,34 @@ def main():
         if multi:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sync_all()
+        if comm is not None:
+            comm.check()
         return float(t.item())
 
+    state["stage"] = "warm-up"
     for i in range(warmup):
         step(i)
     sync_all()
     if comm is not None:
         comm.check()
 
+    state["stage"] = "timed region"
     sampler = ClockSampler(local) if rank == 0 else None
     launches0 = comm.launches if comm is not None else 0
     if sampler:
         sampler.start()
         time.sleep(0.25)
     seconds = timed(step, steps)
-    # keep the GPU busy a little longer so that the 100 ms sampler sees the loaded clocks
-    t_end = time.time() + 0.6
-    extra = 0
-    while time.time() < t_end:
-        step(extra)
-        extra += 1
-        if extra % 16 == 0:
+    # Keep the GPU busy a little longer so that the 100 ms sampler sees the loaded clocks.  Every step is
+    # a collective, so every rank must issue the SAME number of extra steps: the count comes from
+    # `seconds`, which is already the maximum over ranks and therefore identical everywhere.
+    state["stage"] = "clock sampling tail"
+    extra = int(min(20000, max(16, math.ceil(0.6 / max(seconds / steps, 1e-6)))))
+    for i in range(extra):
+        step(i)
+        if i % 64 == 63:
             torch.cuda.synchronize()
-    torch.cuda.synchronize()
+    sync_all()
     clocks = sampler.stop() if sampler else None
     launches = (comm.launches - launches0 - extra) if comm is not None else 0
     if comm is not None:
@@ -244,7 +277,23 @@ def main():
     headline_algo = (comm.last_info.sched + ":" + comm.last_info.proto) if comm is not None else "nccl"
     value = busbw(nbytes, seconds / steps, emu_world)
 
+    # ---- the comparison baseline for the same step: NCCL, same loop, same rotating-buffer discipline ----
+    state["stage"] = "NCCL baseline of the headline step"
+    nccl_headline = None
+    if multi and args.impl == "ours":
+        nb = [torch.empty(n, dtype=torch.float16, device="cuda").normal_(0, 1e-3) for _ in range(nbuf)]
+
+        def nccl_head(i):
+            dist.all_reduce(nb[i % nbuf])
+
+        for i in range(warmup):
+            nccl_head(i)
+        s_n = timed(nccl_head, steps)
+        nccl_headline = {"ms_per_step": round(s_n / steps * 1e3, 5), "busbw": round(busbw(nbytes, s_n / steps, world), 3)}
+        del nb
+
     # ---- end to end through the public API: pinned host -> device, all-reduce, device -> host --------
+    state["stage"] = "end-to-end"
     e2e = None
     if args.impl == "ours":
         host_in = [torch.empty(n, dtype=torch.float16).pin_memory() for _ in range(2)]
@@ -271,43 +320,87 @@ def main():
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 2048}
 
     # ---- extras: small-message latency and a few sizes, ours vs NCCL, outside the headline region ----
+    # Both arms are replays of a CUDA graph holding `reps` back-to-back collectives, so that the host cost of
+    # either library's Python entry point is out of the number; the figure is device time per collective,
+    # median of three replays, max over ranks.
     sweep = None
     if not args.no_sweep and args.impl == "ours":
+        state["stage"] = "size sweep"
         sweep = []
-        for e in (10, 12, 14, 16, 18, 20, 22, 24, 26):
+
+        def graph_time(fn, reps):
+            """Median over three replays of a graph of `reps` calls of fn(i); seconds per call, max over ranks."""
+            for i in range(3):
+                fn(i)
+            sync_all()
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for i in range(reps):
+                        fn(i)
+                runner = g.replay
+            except Exception:  # noqa: BLE001 - capture not possible for this arm: time the plain loop
+                g = None
+                torch.cuda.synchronize()
+
+                def runner():
+                    for i in range(reps):
+                        fn(i)
+            runner()
+            ts = [timed(lambda _i: runner(), 1) / reps for _ in range(3)]
+            return statistics.median(ts), g is not None
+
+        gcomm = None
+        if multi:
+            # sequence numbers kept on the device, so that a captured launch stays valid when replayed
+            gcomm = Communicator.from_torch_distributed(local, staging_bytes=(2 << 26) * 2 + (64 << 20), nvls=not args.no_nvls,
+                                                        device_seq=True)
+        c = gcomm if gcomm is not None else comm
+        pool = [c.empty([1 << 26], torch.float16) for _ in range(2)]  # slices of these are symmetric too
+
+        def view(k, m):
+            p, off = pool[k % 2], (k // 2) * m
+            return [t[off:off + m] for t in p] if isinstance(p, list) else p[off:off + m]
+
+        for e in (10, 12, 14, 16, 18, 20, 22, 23, 24, 26):
             m = 1 << e
-            if m <= n:  # slices of the symmetric buffers (same offset on every rank)
-                views = [[t[:m] for t in b] if isinstance(b, list) else b[:m] for b in bufs]
-            else:
-                views = [comm.empty([m], torch.float16) for _ in range(2)]
-            reps = 200 if e <= 18 else (50 if e <= 22 else 20)
+            views = [view(k, m) for k in range(2 if e > 22 else 4)]
+            reps = 100 if e <= 18 else (20 if e <= 22 else 8)
 
-            def ours_step(i, views=views):
+            def ours_step(i, views=views, c=c):
                 if multi:
-                    comm.all_reduce_(views[i % len(views)], args.algo)
+                    c.all_reduce_(views[i % len(views)], args.algo)
                 else:
-                    comm.all_reduce(views[i % len(views)], None, args.algo)
+                    c.all_reduce(views[i % len(views)], None, args.algo)
 
-            for i in range(5):
-                ours_step(i)
-            t_ours = timed(ours_step, reps) / reps
-            comm.all_reduce(views[0], None, args.algo)  # the reporting path, to learn which algorithm ran
-            row = {"elements": m, "bytes": m * 2, "algo": comm.last_info.sched + ":" + comm.last_info.proto,
-                   "ours_us": round(t_ours * 1e6, 3), "ours_busbw": round(busbw(m * 2, t_ours, emu_world), 3)}
             if multi:
-                tv = [torch.zeros(m, dtype=torch.float16, device="cuda") for _ in range(4)]
+                t_ours, graphed = graph_time(ours_step, reps)
+            else:
+                for i in range(5):
+                    ours_step(i)
+                t_ours, graphed = statistics.median([timed(ours_step, reps) / reps for _ in range(3)]), False
+            c.all_reduce(views[0], None, args.algo)  # the reporting path, to learn which algorithm ran
+            row = {"elements": m, "bytes": m * 2, "algo": c.last_info.sched + ":" + c.last_info.proto,
+                   "ours_us": round(t_ours * 1e6, 3), "ours_busbw": round(busbw(m * 2, t_ours, emu_world), 3),
+                   "timing": "cuda-graph replay" if graphed else "launch loop"}
+            if multi:
+                tv = [torch.zeros(m, dtype=torch.float16, device="cuda") for _ in range(len(views))]
 
                 def nccl_step(i, tv=tv):
-                    dist.all_reduce(tv[i % 4])
+                    dist.all_reduce(tv[i % len(tv)])
 
-                for i in range(5):
-                    nccl_step(i)
-                t_nccl = timed(nccl_step, reps) / reps
+                t_nccl, n_graphed = graph_time(nccl_step, reps)
                 row["nccl_us"] = round(t_nccl * 1e6, 3)
                 row["nccl_busbw"] = round(busbw(m * 2, t_nccl, world), 3)
+                row["nccl_timing"] = "cuda-graph replay" if n_graphed else "launch loop"
+                del tv
             sweep.append(row)
+        if gcomm is not None:
+            gcomm.check()
+            gcomm.close()
         comm.check()
 
+    state["stage"] = "report"
     if rank == 0:
         out = {
             "metric": METRIC,
@@ -319,7 +412,9 @@ def main():
             "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": True,
             "scaling": "weak",
-            "vs_baseline": None,
+            # the reference publishes no number; the comparison baseline is NCCL's all-reduce of the same step
+            # on the same GPUs in the same run (none exists for a world of one GPU)
+            "vs_baseline": round(value / nccl_headline["busbw"], 3) if nccl_headline else None,
             "dtype": "fp16",
             "data": "synthetic N(0,1e-3) seeded by rank",
             "impl": args.impl,
@@ -332,6 +427,8 @@ def main():
                 "algo": f"{args.algo} -> {headline_algo}",
                 "buffers": f"{nbuf} rotating buffers = {nbuf * nbytes >> 20} MiB > 126 MiB L2, in place, symmetric heap (no staging copy)",
                 "busbw": "bytes/time*2(n-1)/n, device time by CUDA events, max over ranks",
+                "baseline": ("NCCL all-reduce of the same step, same run: " + json.dumps(nccl_headline)) if nccl_headline else
+                            "none at one GPU (NCCL has no peer)",
             },
             "clocks": clocks,
             "gpu_launches": launches,
@@ -345,6 +442,7 @@ def main():
             out["config"]["backing"] = comm.backing
         json_out.write(json.dumps(out) + "\n")
         json_out.flush()
+    state["stage"] = "teardown"
     if comm is not None:
         comm.close()
     if multi:

@@ -52,6 +52,16 @@ void wait_io(int fd, short events, Clock::time_point deadline, const char* what)
   }
 }
 
+// Abstract-namespace sockets carry no file permissions, so anyone on the machine could dial or
+// squat a name.  The kernel tells who is at the other end: only a process of the same user may
+// take part in the exchange of memory descriptors.
+bool peer_is_same_user(int fd) {
+  ucred cred{};
+  socklen_t len = sizeof(cred);
+  if (::getsockopt(fd, SOL_SOCKET, SO_PEERCRED, &cred, &len) != 0) return false;
+  return cred.uid == ::getuid();
+}
+
 const char* env_or_null(const char* k) {
   const char* v = std::getenv(k);
   return (v && *v) ? v : nullptr;
@@ -87,6 +97,11 @@ UnixMesh::UnixMesh(int rank, int world, const MeshOptions& opt)
       int fd = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
       B200_SYS_CHECK(fd);
       if (::connect(fd, reinterpret_cast<sockaddr*>(&paddr), plen) == 0) {
+        if (!peer_is_same_user(fd)) {
+          ::close(fd);
+          B200_REQUIRE(false, "the bootstrap socket of rank " << peer << " belongs to another user; refusing to exchange "
+                                                                 "memory handles with it");
+        }
         int32_t me = rank;
         conn_[size_t(peer)] = fd;
         send_all(peer, &me, sizeof(me));
@@ -107,6 +122,11 @@ UnixMesh::UnixMesh(int rank, int world, const MeshOptions& opt)
     wait_io(listen_fd_, POLLIN, deadline, "accept a peer");
     int fd = ::accept4(listen_fd_, nullptr, nullptr, SOCK_CLOEXEC);
     B200_SYS_CHECK(fd);
+    if (!peer_is_same_user(fd)) {  // not one of this job's ranks: drop it and keep waiting
+      ::close(fd);
+      --n;
+      continue;
+    }
     int32_t who = -1;
     size_t got = 0;
     while (got < sizeof(who)) {

@@ -4,6 +4,7 @@
 #include "no_alloc.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -80,6 +81,17 @@ extern "C" int b200ipc_allreduce_noalloc(const void* const* ins, void* const* ou
 
   const void* fn = dtype == 0 ? kernel_for<__half>(world) : kernel_for<__nv_bfloat16>(world);
 
+  // Two knobs read from the environment, for tests of the failure report: the time limit of a
+  // device-side wait (B200IPC_TIMEOUT_US, as everywhere in the library) and a rank that sends
+  // nothing (B200IPC_NOALLOC_MUTE_RANK), which makes the others' bounded waits run out.
+  uint64_t timeout_ns = 2000000000ull;
+  if (const char* t = std::getenv("B200IPC_TIMEOUT_US")) {
+    const long long us = std::atoll(t);
+    if (us > 0) timeout_ns = uint64_t(us) * 1000ull;
+  }
+  int mute_rank = -1;
+  if (const char* m = std::getenv("B200IPC_NOALLOC_MUTE_RANK")) mute_rank = std::atoi(m);
+
   // Geometry: as many CTAs per rank as the barrier pads, the work and co-residency allow.
   int per_sm = 0, sms = 0;
   e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kBulkThreads, 0);
@@ -115,8 +127,11 @@ extern "C" int b200ipc_allreduce_noalloc(const void* const* ins, void* const* ou
     v.in = ins[r];
     v.out = outs[r];
     v.nelems = nelems;
-    v.status = reinterpret_cast<StatusBlock*>(v.heap + kStatusOff);
-    v.timeout_ns = 2000000000ull;
+    // ONE record for the whole emulated world (the one in rank 0's region): whichever rank's wait
+    // runs out first writes it, and that is the record copied back to the caller below.
+    v.status = reinterpret_cast<StatusBlock*>(base + kStatusOff);
+    v.timeout_ns = timeout_ns;
+    if (r == mute_rank) v.flags |= kMuteSends;
     v.bar_seq = 0;
     v.aux[0] = kCtrlRegion;                  // staging area inside each rank's region
     v.aux[1] = kBulkCopyIn | kBulkCopyOut;   // the caller's buffers are ordinary memory

@@ -32,7 +32,10 @@
 //
 // dtype: 0 = fp16, 1 = bf16.  status_host may be null; otherwise 8 words are copied to it
 // (stream-ordered, after the kernel): {code, rank, peer, cta, step, expected, seen, site},
-// code 0 = fine, 1 = a bounded device-side wait ran out.
+// code 0 = fine, 1 = a bounded device-side wait ran out (2 s, or B200IPC_TIMEOUT_US microseconds when that
+// environment variable is set), 2 = a rank stopped because another one had given up.  All emulated ranks
+// share this one record.  A return value of 0 together with a non-zero code means that the kernel ended
+// early: the contents of outs are then undefined.
 //
 // Returns 0 on success, 1 for a bad argument, 2 when nelems exceeds the maximum,
 // 100 + cudaError_t when a CUDA call failed.

@@ -83,6 +83,7 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapL
       if (int32_t(seen - value) >= 0) break;
       if ((++spins & 0x3fu) == 0) {
         if (ld_volatile_u32(abort_word) != 0) {
+          note_aborted_by_peer(me.status, me.rank, site);
           s_fail = 1;
           break;
         }

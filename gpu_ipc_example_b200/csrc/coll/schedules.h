@@ -27,7 +27,9 @@
 // and a context Cx with the rank's pointers plus
 //   bool Cx::wait(Msg&, const char* src, uint32 flag, int site, int peer, int step)
 // which spins on try_recv under a time limit and returns false when the
-// collective has been aborted (the wire then returns at once).
+// collective has been aborted (the wire then returns at once), and
+//   bool Cx::wait_many(Msg (&m)[CNT], src[CNT], pending bits, flag, site, peer[CNT], step)
+// which does the same for several transactions whose polls may overlap.
 //
 // Capability parity (schedules): parallel_transmit.hpp:62-132 (two-phase,
 // sub-group parallel), sequential_transmit.hpp:82-208 (one sub-group serves all
@@ -129,6 +131,13 @@ struct Ctx {
                     int64_t step) const {
     return B::wait(waiter, m, src, flag, site, peer, step, rank);
   }
+  // Waits for every transaction whose bit is set in `pending` (m[i] from src[i], sent by rank peer[i]);
+  // on the GPU the polls of all of them overlap.
+  template <int CNT>
+  B200_HD bool wait_many(typename B::Msg (&m)[CNT], const char* const (&src)[CNT], uint32_t pending, uint32_t flag,
+                         int site, const int (&peer)[CNT], int64_t step) const {
+    return B::template wait_many<CNT>(waiter, m, src, pending, flag, site, peer, step, rank);
+  }
 };
 
 #define B200_WAIT(c, m, src, flag, site, peer, step) \
@@ -169,13 +178,17 @@ B200_HD void run_parallel(const Ctx<B>& c, int wire) {
     } else {
       typename B::Acc a;
       B::acc_init(a, v);
+      typename B::Msg m[N];
+      const char* src[N];
+      int from[N];
 #pragma unroll
-      for (int i = 1; i < N; ++i) {
-        const int q = (r + i) % N;
-        typename B::Msg m;
-        B200_WAIT(c, m, txn_at<B>(c.sink(0), (int64_t(g) * N + q) * kParallelSlots + slot), flag, 0, q, t);
-        B::acc_add(a, m, c.round_each());
+      for (int i = 0; i < N; ++i) {
+        from[i] = (r + i) % N;
+        src[i] = txn_at<B>(c.sink(0), (int64_t(g) * N + from[i]) * kParallelSlots + slot);
       }
+      if (!c.wait_many(m, src, (1u << N) - 2u, flag, 0, from, t)) return;
+#pragma unroll
+      for (int i = 1; i < N; ++i) B::acc_add(a, m[i], c.round_each());
       B::acc_to_msg(v, a);
       B::set_flags(v, flag);
 #pragma unroll
@@ -222,13 +235,17 @@ B200_HD void run_sequential(const Ctx<B>& c, int wire) {
     B::shuffle(v);
     typename B::Acc a;
     B::acc_init(a, v);
+    typename B::Msg m[N];
+    const char* src[N];
+    int from[N];
 #pragma unroll
-    for (int i = 1; i < N; ++i) {
-      const int q = (r + i) % N;
-      typename B::Msg m;
-      B200_WAIT(c, m, txn_at<B>(c.sink(0), idx(q)), flag, 0, q, t);
-      B::acc_add(a, m, c.round_each());
+    for (int i = 0; i < N; ++i) {
+      from[i] = (r + i) % N;
+      src[i] = txn_at<B>(c.sink(0), idx(from[i]));
     }
+    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 0, from, t)) return;
+#pragma unroll
+    for (int i = 1; i < N; ++i) B::acc_add(a, m[i], c.round_each());
     B::acc_to_msg(v, a);
     B::set_flags(v, flag);
 #pragma unroll
@@ -239,12 +256,12 @@ B200_HD void run_sequential(const Ctx<B>& c, int wire) {
     B::restore(v);
     B::store(c.out, int64_t(r) * p.chunk_dw + off, chunk_end(r), p.odd_dw, v);
 #pragma unroll
+    for (int i = 0; i < N; ++i) src[i] = txn_at<B>(c.sink(1), idx(from[i]));
+    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 1, from, t)) return;
+#pragma unroll
     for (int i = 1; i < N; ++i) {
-      const int q = (r + i) % N;
-      typename B::Msg m;
-      B200_WAIT(c, m, txn_at<B>(c.sink(1), idx(q)), flag, 1, q, t);
-      B::restore(m);
-      B::store(c.out, int64_t(q) * p.chunk_dw + off, chunk_end(q), p.odd_dw, m);
+      B::restore(m[i]);
+      B::store(c.out, int64_t(from[i]) * p.chunk_dw + off, chunk_end(from[i]), p.odd_dw, m[i]);
     }
   }
 }
@@ -389,13 +406,19 @@ B200_HD void run_direct_allgather(const Ctx<B>& c, int wire) {
       const int q = (r + i) % N;
       c.send(txn_at<B>(c.peer_sink(1, q), idx(r)), v);
     }
+    typename B::Msg m[N];
+    const char* src[N];
+    int from[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      from[i] = (r + i) % N;
+      src[i] = txn_at<B>(c.sink(1), idx(from[i]));
+    }
+    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 1, from, t)) return;
 #pragma unroll
     for (int i = 1; i < N; ++i) {
-      const int q = (r + i) % N;
-      typename B::Msg m;
-      B200_WAIT(c, m, txn_at<B>(c.sink(1), idx(q)), flag, 1, q, t);
-      B::restore(m);
-      B::store(c.out, int64_t(q) * shard_dw + off, int64_t(q + 1) * shard_dw, -1, m);
+      B::restore(m[i]);
+      B::store(c.out, int64_t(from[i]) * shard_dw + off, int64_t(from[i] + 1) * shard_dw, -1, m[i]);
     }
   }
 }
@@ -458,14 +481,18 @@ B200_HD void run_bisect(const Ctx<B>& c, int wire) {
       B200_WAIT(c, v, txn_at<B>(c.sink(1), (int64_t(g) * BI + y) * kParallelSlots + slot), flag, 1,
                 2 * y + parity, t);
     } else {
+      typename B::Msg m[BI];
+      const char* src[BI];
+      int from[BI];
 #pragma unroll
-      for (int i = 1; i < BI; ++i) {
+      for (int i = 0; i < BI; ++i) {
         const int ql = (l + i) % BI;
-        typename B::Msg m;
-        B200_WAIT(c, m, txn_at<B>(c.sink(0), (int64_t(g) * BI + ql) * kParallelSlots + slot), flag, 0,
-                  2 * ql + parity, t);
-        B::acc_add(a, m, c.round_each());
+        from[i] = 2 * ql + parity;
+        src[i] = txn_at<B>(c.sink(0), (int64_t(g) * BI + ql) * kParallelSlots + slot);
       }
+      if (BI > 1 && !c.wait_many(m, src, (1u << BI) - 2u, flag, 0, from, t)) return;
+#pragma unroll
+      for (int i = 1; i < BI; ++i) B::acc_add(a, m[i], c.round_each());
       B::acc_to_msg(v, a);
       B::set_flags(v, flag);
 #pragma unroll
@@ -517,22 +544,22 @@ B200_HD void run_oneshot(const Ctx<B>& c, int wire) {
       const int q = (r + i) % N;
       c.send(at(c.peer_oneshot(q), r), v);
     }
+    // all world - 1 landing slots are polled together; m[q] is rank q's slice, own slice at m[r]
     typename B::Acc a;
-    typename B::Msg m;
-    if (r == 0) {
-      B::acc_init(a, v);
-    } else {
-      B200_WAIT(c, m, at(c.oneshot(), 0), flag, 4, 0, t);
-      B::acc_init(a, m);
-    }
+    typename B::Msg m[N];
+    const char* src[N];
+    int from[N];
 #pragma unroll
-    for (int q = 1; q < N; ++q) {
-      if (q == r) {
-        B::acc_add(a, v, c.round_each());
-      } else {
-        B200_WAIT(c, m, at(c.oneshot(), q), flag, 4, q, t);
-        B::acc_add(a, m, c.round_each());
-      }
+    for (int q = 0; q < N; ++q) {
+      from[q] = q;
+      src[q] = at(c.oneshot(), q);
+    }
+    if (!c.wait_many(m, src, ((1u << N) - 1u) & ~(1u << r), flag, 4, from, t)) return;
+#pragma unroll
+    for (int q = 0; q < N; ++q) {
+      if (q == r) m[q] = v;  // flag dwords differ from a received copy, but no accumulator slot reads them
+      if (q == 0) B::acc_init(a, m[q]);
+      else B::acc_add(a, m[q], c.round_each());
     }
     B::acc_to_msg(v, a);
     B::restore(v);

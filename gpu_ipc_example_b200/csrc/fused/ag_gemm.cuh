@@ -124,7 +124,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
             const uint32_t seen = ld_acquire_sys_u32(arrived + q);
             if (int32_t(seen - args.arrive_target) >= 0) break;
             if ((++spins & 0x3fu) == 0) {
-              if (ld_volatile_u32(abort_word) != 0) { ok = false; break; }
+              if (ld_volatile_u32(abort_word) != 0) {
+                note_aborted_by_peer(me.status, rank, 30);
+                ok = false;
+                break;
+              }
               const uint64_t now = globaltimer_ns();
               if (t0 == 0) t0 = now;
               else if (now - t0 > me.timeout_ns) {

@@ -211,6 +211,7 @@ struct RowCtx {
         if (seen == seq) break;
         if ((++spins & 0x3fu) == 0) {
           if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
+            if (ld_volatile_u32(abort_word) != 0) note_aborted_by_peer(me->status, me->rank, 21);
             *fail = 1;
             ok = false;
             break;
@@ -612,7 +613,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       const uint32_t seen = ld_acquire_sys_u32(done);
       if (int32_t(seen - done_target) >= 0) break;
       if ((++spins & 0x3fu) == 0) {
-        if (ld_volatile_u32(abort_word) != 0) break;
+        if (ld_volatile_u32(abort_word) != 0) {
+          note_aborted_by_peer(me.status, rank, 22);
+          break;
+        }
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) t0 = now;
         else if (now - t0 > me.timeout_ns) {

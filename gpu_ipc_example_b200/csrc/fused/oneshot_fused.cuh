@@ -104,26 +104,26 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
         }
       }
     }
+    // all world - 1 landing slots are polled together (a poll is a round trip to L2)
     typename B::Acc a;
-    typename B::Msg m;
-    if (r == 0) {
-      B::acc_init(a, v);
-    } else {
-      ok = B::wait(waiter, m, at(me.heap, 0), flag, 5, 0, k, r);
+    typename B::Msg m[N];
+    if (N > 1) {
+      const char* src[N];
+      int from[N];
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        from[q] = q;
+        src[q] = at(me.heap, q);
+      }
+      ok = B::template wait_many<N>(waiter, m, src, ((1u << N) - 1u) & ~(1u << r), flag, 5, from, k, r);
       if (!ok) break;
-      B::acc_init(a, m);
     }
 #pragma unroll
-    for (int q = 1; q < N; ++q) {
-      if (q == r) {
-        B::acc_add(a, v, false);
-      } else {
-        ok = B::wait(waiter, m, at(me.heap, q), flag, 5, q, k, r);
-        if (!ok) break;
-        B::acc_add(a, m, false);
-      }
+    for (int q = 0; q < N; ++q) {
+      if (q == r) m[q] = v;
+      if (q == 0) B::acc_init(a, m[q]);
+      else B::acc_add(a, m[q], false);
     }
-    if (!ok) break;
 
     if (EPI == kEpiNorm) {
       typename B::Msg rv;

@@ -53,6 +53,19 @@ __device__ __forceinline__ void st_volatile_v4(void* p, const uint32_t (&d)[4]) 
                : "memory");
 }
 
+// A wait that gave up because ANOTHER wire or rank raised the abort word: leave a trace in this
+// rank's status block (pinned host memory) unless a more specific record is already there, so that
+// the host's check raises on every rank of an aborted collective, not only on the one that timed out.
+__device__ __forceinline__ void note_aborted_by_peer(StatusBlock* s, int rank, int site) {
+  if (ld_volatile_u32(&s->code) == kOk) {
+    s->rank = uint32_t(rank);
+    s->where = uint32_t(site);
+    __threadfence_system();
+    s->code = kAbortedByPeer;
+    __threadfence_system();
+  }
+}
+
 struct DevWaiter {
   const RankView* me;  // kernel parameter space
   size_t ctrl_off;
@@ -237,25 +250,86 @@ struct DevBackend : WireFormat<K> {
       st_volatile_v4(p, v.d);
     }
   }
-  // Loads the transaction; returns true (to the whole warp) when every flag matches.
-  __device__ static bool try_recv(Msg& v, const char* src, uint32_t flag) {
-    const int l = lane();
-    const char* p = src + l * (kLaneDw * 4);
-    bool ok;
-    if constexpr (K == ProtoKind::LL8) {
-      ld_volatile_v2(p, v.d[0], v.d[1]);
-      ok = (v.d[1] == flag);
-    } else if constexpr (K == ProtoKind::LL16) {
-      ld_volatile_v4(p, v.d);
-      ok = (v.d[1] == flag) && (v.d[3] == flag);
-    } else if constexpr (K == ProtoKind::LL128) {
+  // The receive side in two halves, so that a wire expecting several transactions can have all
+  // their loads in flight before it looks at any flag (a poll is a round trip to L2).
+  __device__ static void recv_load(Msg& v, const char* src) {
+    const char* p = src + lane() * (kLaneDw * 4);
+    if constexpr (kLaneDw == 1) {
       v.d[0] = ld_volatile_u32(p);
-      ok = !(l == 15 || l == 31) || (v.d[0] == flag);
+    } else if constexpr (kLaneDw == 2) {
+      ld_volatile_v2(p, v.d[0], v.d[1]);
     } else {
       ld_volatile_v4(p, v.d);
-      ok = ((l & 3) != 3) || (v.d[3] == flag);
     }
-    return __all_sync(0xffffffffu, ok);
+  }
+  // This lane's verdict on its part of the transaction.
+  __device__ static bool recv_ok(const Msg& v, uint32_t flag) {
+    const int l = lane();
+    if constexpr (K == ProtoKind::LL8) {
+      return v.d[1] == flag;
+    } else if constexpr (K == ProtoKind::LL16) {
+      return (v.d[1] == flag) && (v.d[3] == flag);
+    } else if constexpr (K == ProtoKind::LL128) {
+      return !(l == 15 || l == 31) || (v.d[0] == flag);
+    } else {
+      return ((l & 3) != 3) || (v.d[3] == flag);
+    }
+  }
+  // Loads the transaction; returns true (to the whole warp) when every flag matches.
+  __device__ static bool try_recv(Msg& v, const char* src, uint32_t flag) {
+    recv_load(v, src);
+    return __all_sync(0xffffffffu, recv_ok(v, flag));
+  }
+
+  // Waits for several transactions at once: bit i of `pending` set = m[i] is still expected from
+  // src[i] (sent by rank peer[i]).  Every round issues the loads of all pending transactions
+  // back to back and only then tests them, so the round trips overlap instead of adding up.
+  template <int CNT>
+  __device__ static bool wait_many(const DevWaiter& w, Msg (&m)[CNT], const char* const (&src)[CNT], uint32_t pending,
+                                   uint32_t flag, int site, const int (&peer)[CNT], int64_t step, int rank) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+#pragma unroll
+      for (int i = 0; i < CNT; ++i)
+        if (pending & (1u << i)) recv_load(m[i], src[i]);
+      uint32_t mine = 0;
+#pragma unroll
+      for (int i = 0; i < CNT; ++i)
+        if ((pending & (1u << i)) && recv_ok(m[i], flag)) mine |= 1u << i;
+      pending &= ~__reduce_and_sync(0xffffffffu, mine | ~pending);
+      if (pending == 0) return true;
+      if ((++spins & 0xffu) == 0) {
+        int give_up = 0;
+        if (lane() == 0) {
+          if (ld_volatile_u32(w.abort_word()) != 0) {
+            give_up = 1;
+          } else {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+              t0 = now;
+            } else if (now - t0 > w.me->timeout_ns) {
+              give_up = 2;
+            }
+          }
+        }
+        give_up = __shfl_sync(0xffffffffu, give_up, 0);
+        if (give_up) {
+          const int first = __ffs(int(pending)) - 1;
+          int who = peer[0];
+          const char* where = src[0];
+#pragma unroll
+          for (int i = 1; i < CNT; ++i)
+            if (i == first) {
+              who = peer[i];
+              where = src[i];
+            }
+          if (give_up == 2) report_timeout(w, where, flag, site, who, step, rank);
+          else if (lane() == 0) note_aborted_by_peer(w.me->status, rank, site);
+          return false;
+        }
+      }
+    }
   }
 
   __device__ static bool wait(const DevWaiter& w, Msg& v, const char* src, uint32_t flag, int site, int peer,
@@ -281,6 +355,7 @@ struct DevBackend : WireFormat<K> {
         give_up = __shfl_sync(0xffffffffu, give_up, 0);
         if (give_up) {
           if (give_up == 2) report_timeout(w, src, flag, site, peer, step, rank);
+          else if (lane() == 0) note_aborted_by_peer(w.me->status, rank, site);
           return false;
         }
       }

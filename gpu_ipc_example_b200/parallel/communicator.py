@@ -275,6 +275,11 @@ class Communicator:
         return ts if self._virtual else ts[0]
 
     def free_symmetric(self):
+        """Releases every symmetric allocation at once.  Tensors handed out by `empty()` before, and the
+        outputs of earlier `linear_allreduce` / `allgather_linear` calls (whose cached workspaces live in
+        the same region), become invalid: the next allocations reuse their memory."""
+        self.__dict__.pop("_gemm_buffers", None)
+        self.__dict__.pop("_ag_buffers", None)
         self._C.sym_free_all(self._h)
 
     # ------------------------------------------------------------------ state

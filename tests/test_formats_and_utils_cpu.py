@@ -68,3 +68,27 @@ def test_tuner_picks_the_fastest_algorithm_per_size():
     assert merged == [(2048, "oneshot:ll512"), (0, "parallel:ll512")]
     cpp = tune.as_cpp(merged)
     assert "{2 * KiB, SchedKind::OneShot, ProtoKind::LL512}," in cpp and "{0, SchedKind::Parallel, ProtoKind::LL512}," in cpp
+
+
+def test_tuner_reads_json_rows_and_limits_the_row_count():
+    import json
+
+    from gpu_ipc_example_b200 import tune
+
+    nine = tune.parse_sweep("  1024 2048 1 8 9.00 10.00 12.00 0.2 0.4\n")
+    assert nine == {1024: 10.0}  # the median column of the nine-column table
+    rows = []
+    times = {"oneshot:ll512": [5, 6, 9, 30, 90, 300], "parallel:ll512": [8, 8, 8.5, 12, 40, 150], "bisect:ll512": [9, 9, 9, 11.9, 41, 151],
+             "nvls": [17, 17, 17, 18, 25, 60]}
+    for algo, ts in times.items():
+        for e, us in zip((10, 12, 14, 16, 18, 20), ts):
+            rows.append(json.dumps({"collective": "all_reduce", "algo": algo, "world": 8, "placement": "in_place", "symmetric": False,
+                                    "elements": 1 << e, "us_median": us}))
+    rows.append(json.dumps({"collective": "all_reduce", "algo": "nvls", "world": 4, "placement": "in_place", "symmetric": False,
+                            "elements": 1024, "us_median": 1.0}))
+    tables = tune.parse_json_rows("\n".join(rows), 8)
+    assert set(tables) == set(times) and tables["nvls"][1024] == 17
+    every = tune.merge_rows(tune.best_per_size(tables))
+    assert [a for _, a in every] == ["oneshot:ll512", "parallel:ll512", "bisect:ll512", "nvls"]
+    three = tune.best_table(tables, 3)
+    assert three == [(2 << 12, "oneshot:ll512"), (2 << 16, "parallel:ll512"), (0, "nvls")]
