@@ -59,10 +59,29 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
                : "memory");
 }
 
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // Barrier between CTA `blockIdx.x` of every rank.  All threads call it; returns
 // false (to all threads) if the wait ran out or the collective was aborted.
+// `publish` = this CTA has written something the other ranks are about to read (its
+// signal must then be a release); an arrival that only says "my kernel has started" is a
+// plain store.  The polls are relaxed loads, and what the other ranks published is read
+// afterwards with loads that go around L1 (ld.volatile / multimem), issued after the poll
+// has returned: no acquire fence is paid for.
 __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapLayout& lay, uint32_t value,
-                                                 int site) {
+                                                 int site, bool publish) {
   __shared__ int s_fail;
   const int tid = int(threadIdx.x);
   if (tid == 0) s_fail = 0;
@@ -70,20 +89,22 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapL
   const size_t pad_off = lay.ctrl_off + kCtrlBarrierOff + size_t(blockIdx.x) * kMaxRanks * sizeof(uint32_t);
   if (tid < me.world && tid != me.rank) {
     uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
-    // st.release.sys is the only fence: it orders the CTA's earlier accesses (made visible to this
-    // thread by the barrier above) before the signal
     if (!(me.flags & kMuteSends)) {
-      st_release_sys_u32(reinterpret_cast<uint32_t*>(me.peer[tid] + pad_off) + me.rank, value);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(me.peer[tid] + pad_off) + me.rank;
+      // st.release.sys orders the CTA's earlier accesses (made visible to this thread by the
+      // barrier above) before the signal
+      if (publish) st_release_sys_u32(dst, value);
+      else st_relaxed_sys_u32(dst, value);
     }
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(me.heap + pad_off) + tid;
     uint32_t spins = 0;
     uint64_t t0 = 0;
     for (;;) {
-      uint32_t seen = ld_acquire_sys_u32(mine);
+      uint32_t seen = ld_relaxed_sys_u32(mine);
       if (int32_t(seen - value) >= 0) break;
       if ((++spins & 0x3fu) == 0) {
         if (ld_volatile_u32(abort_word) != 0) {
-          note_aborted_by_peer(me.status, me.rank, site);
+          note_aborted_by_peer(abort_word, me.status, me.rank, site);
           s_fail = 1;
           break;
         }
@@ -91,7 +112,7 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapL
         if (t0 == 0) {
           t0 = now;
         } else if (now - t0 > me.timeout_ns) {
-          if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+          if (claim_status(abort_word, kTimeout)) {
             StatusBlock* s = me.status;
             s->rank = uint32_t(me.rank);
             s->peer = uint32_t(tid);
@@ -104,9 +125,8 @@ __device__ __forceinline__ bool cta_rank_barrier(const RankView& me, const HeapL
             s->code = kTimeout;
             __threadfence_system();
           }
-          for (int q = 0; q < me.world; ++q)
-            if (q != me.rank)
-              st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[q] + lay.ctrl_off + kCtrlAbortOff), 1u);
+          for (int q = 0; q < me.world; ++q)  // own abort word included
+            st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[q] + lay.ctrl_off + kCtrlAbortOff), 1u);
           s_fail = 1;
           break;
         }
@@ -220,7 +240,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
   }
   // Every rank has arrived (so it has left the previous collective and, for the
   // reducing modes, its input is in place) before any remote access.
-  if (!cta_rank_barrier(me, lay, bar + 1, 10)) return;
+  if (!cta_rank_barrier(me, lay, bar + 1, 10, /*publish=*/copy_in)) return;
 
   // ---- phase 1: the collective ---------------------------------------------------
   if (M == BulkMode::AllGather) {
@@ -268,7 +288,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
           if (i < shard_vec) {
             const size_t off = sym_off + size_t(int64_t(r) * shard_vec + i) * 16;
 #pragma unroll
-            for (int q = 0; q < N; ++q) v[u][q] = *reinterpret_cast<const uint4*>(me.peer[q] + off);
+            for (int q = 0; q < N; ++q) v[u][q] = ld_volatile_u4(me.peer[q] + off);
           }
         }
 #pragma unroll
@@ -302,7 +322,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
   }
 
   // ---- phase 2: everyone's loads and stores are done ---------------------------------
-  if (!cta_rank_barrier(me, lay, bar + 2, 11)) return;
+  if (!cta_rank_barrier(me, lay, bar + 2, 11, /*publish=*/true)) return;
 
   // ---- phase 3: hand the result to the caller ----------------------------------------
   if (M != BulkMode::ReduceScatter && copy_out) {
@@ -313,8 +333,7 @@ __global__ void __launch_bounds__(kBulkThreads) bulk_kernel(const __grid_constan
         for (int u = 0; u < kU; ++u) {
           const int64_t i = (tile + int64_t(u) * G) * nthreads + tid;
           if (i < shard_vec && i * 8 < nv)
-            st_vec_guarded(out16 + int64_t(s) * shard_elems, i, nv,
-                           *reinterpret_cast<const uint4*>(my_buf + (int64_t(s) * shard_vec + i) * 16));
+            st_vec_guarded(out16 + int64_t(s) * shard_elems, i, nv, ld_volatile_u4(my_buf + (int64_t(s) * shard_vec + i) * 16));
         }
     }
   }

@@ -197,16 +197,26 @@ StatusBlock Comm::status(int local) const {
 }
 
 void Comm::raise_if_failed() const {
+  // A rank whose own wait ran out knows whom it was waiting for; a rank that was told to stop only
+  // knows that.  Report the first kind if any local rank has it.
+  int pick = -1;
   for (size_t i = 0; i < status_.size(); ++i) {
-    StatusBlock s = status(int(i));
-    if (s.code == kOk) continue;
-    std::ostringstream os;
-    os << "[b200ipc] collective failed on rank " << s.rank << ": "
-       << (s.code == kTimeout ? "bounded wait ran out" : "aborted") << " (site " << s.where << ", waiting for rank "
-       << s.peer << ", wire " << s.wire << ", step " << s.step << ", expected flag 0x" << std::hex << s.expected
-       << ", saw 0x" << s.seen << ")";
-    throw Error(os.str());
+    const uint32_t code = status(int(i)).code;
+    if (code == kOk) continue;
+    if (pick < 0 || (code == kTimeout && status(pick).code != kTimeout)) pick = int(i);
   }
+  if (pick < 0) return;
+  const StatusBlock s = status(pick);
+  std::ostringstream os;
+  os << "[b200ipc] collective failed on rank " << s.rank << ": ";
+  if (s.code == kTimeout) {
+    os << "bounded wait ran out (site " << s.where << ", waiting for rank " << s.peer << ", wire " << s.wire << ", step "
+       << s.step << ", expected flag 0x" << std::hex << s.expected << ", saw 0x" << s.seen << ")";
+  } else {
+    os << "aborted because another wire or rank gave up a bounded wait (site " << s.where
+       << "); its output is incomplete";
+  }
+  throw Error(os.str());
 }
 
 void Comm::reset() {

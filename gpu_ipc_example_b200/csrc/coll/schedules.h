@@ -28,8 +28,8 @@
 //   bool Cx::wait(Msg&, const char* src, uint32 flag, int site, int peer, int step)
 // which spins on try_recv under a time limit and returns false when the
 // collective has been aborted (the wire then returns at once), and
-//   bool Cx::wait_many(Msg (&m)[CNT], src[CNT], pending bits, flag, site, peer[CNT], step)
-// which does the same for several transactions whose polls may overlap.
+//   bool B::wait_many<CNT>(waiter, Msg (&m)[CNT], src(i), peer(i), pending bits, flag, site, step, rank)
+// which does the same for several transactions whose polls may overlap (recv_in_order below).
 //
 // Capability parity (schedules): parallel_transmit.hpp:62-132 (two-phase,
 // sub-group parallel), sequential_transmit.hpp:82-208 (one sub-group serves all
@@ -131,13 +131,6 @@ struct Ctx {
                     int64_t step) const {
     return B::wait(waiter, m, src, flag, site, peer, step, rank);
   }
-  // Waits for every transaction whose bit is set in `pending` (m[i] from src[i], sent by rank peer[i]);
-  // on the GPU the polls of all of them overlap.
-  template <int CNT>
-  B200_HD bool wait_many(typename B::Msg (&m)[CNT], const char* const (&src)[CNT], uint32_t pending, uint32_t flag,
-                         int site, const int (&peer)[CNT], int64_t step) const {
-    return B::template wait_many<CNT>(waiter, m, src, pending, flag, site, peer, step, rank);
-  }
 };
 
 #define B200_WAIT(c, m, src, flag, site, peer, step) \
@@ -145,6 +138,38 @@ struct Ctx {
 
 template <class B>
 B200_HD char* txn_at(char* base, int64_t idx) { return base + idx * B::kTxnBytes; }
+
+// Transactions a wire keeps in registers while their polls overlap.  A poll is a round trip to
+// L2; a wire that expects world - 1 transactions polls them in groups of this size instead of
+// one after the other.
+constexpr int kPollGroup = 4;
+
+// Receives the transactions numbered LO .. HI-1 (number i sits at src(i) and was sent by rank
+// peer(i)) and hands them IN ORDER to use(i, msg).  Number `skip` is not received: `own` is
+// handed over in its place (-1: nothing is skipped).  Returns false when the collective was aborted.
+template <class B, int LO, int HI, class SrcFn, class PeerFn, class UseFn>
+B200_HD bool recv_in_order(const Ctx<B>& c, uint32_t flag, int site, int64_t step, int skip, const typename B::Msg& own,
+                           SrcFn src, PeerFn peer, UseFn use) {
+  if constexpr (LO >= HI) {
+    return true;
+  } else {
+    constexpr int CNT = (HI - LO) < kPollGroup ? (HI - LO) : kPollGroup;
+    typename B::Msg m[CNT];
+    uint32_t pending = (1u << CNT) - 1u;
+    if (skip >= LO && skip < LO + CNT) pending &= ~(1u << (skip - LO));
+    if (pending != 0 &&
+        !B::template wait_many<CNT>(
+            c.waiter, m, [&](int k) { return src(LO + k); }, [&](int k) { return peer(LO + k); }, pending, flag, site,
+            step, c.rank))
+      return false;
+#pragma unroll
+    for (int k = 0; k < CNT; ++k) {
+      if (LO + k == skip) use(LO + k, own);
+      else use(LO + k, m[k]);
+    }
+    return recv_in_order<B, LO + CNT, HI>(c, flag, site, step, skip, own, src, peer, use);
+  }
+}
 
 // ---------------------------------------------------------------------------
 // Parallel two-phase all-reduce.  Wires come in groups of `world`; wire
@@ -178,17 +203,12 @@ B200_HD void run_parallel(const Ctx<B>& c, int wire) {
     } else {
       typename B::Acc a;
       B::acc_init(a, v);
-      typename B::Msg m[N];
-      const char* src[N];
-      int from[N];
-#pragma unroll
-      for (int i = 0; i < N; ++i) {
-        from[i] = (r + i) % N;
-        src[i] = txn_at<B>(c.sink(0), (int64_t(g) * N + from[i]) * kParallelSlots + slot);
-      }
-      if (!c.wait_many(m, src, (1u << N) - 2u, flag, 0, from, t)) return;
-#pragma unroll
-      for (int i = 1; i < N; ++i) B::acc_add(a, m[i], c.round_each());
+      if (!recv_in_order<B, 1, N>(
+              c, flag, 0, t, -1, v,
+              [&](int i) -> const char* { return txn_at<B>(c.sink(0), (int64_t(g) * N + (r + i) % N) * kParallelSlots + slot); },
+              [&](int i) { return (r + i) % N; },
+              [&](int, const typename B::Msg& x) { B::acc_add(a, x, c.round_each()); }))
+        return;
       B::acc_to_msg(v, a);
       B::set_flags(v, flag);
 #pragma unroll
@@ -235,17 +255,15 @@ B200_HD void run_sequential(const Ctx<B>& c, int wire) {
     B::shuffle(v);
     typename B::Acc a;
     B::acc_init(a, v);
-    typename B::Msg m[N];
-    const char* src[N];
-    int from[N];
+    // (this schedule polls its peers one after the other: with world - 1 outgoing and as many
+    // incoming transactions per step already in registers there is no room to overlap the polls)
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-      from[i] = (r + i) % N;
-      src[i] = txn_at<B>(c.sink(0), idx(from[i]));
+    for (int i = 1; i < N; ++i) {
+      const int q = (r + i) % N;
+      typename B::Msg m;
+      B200_WAIT(c, m, txn_at<B>(c.sink(0), idx(q)), flag, 0, q, t);
+      B::acc_add(a, m, c.round_each());
     }
-    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 0, from, t)) return;
-#pragma unroll
-    for (int i = 1; i < N; ++i) B::acc_add(a, m[i], c.round_each());
     B::acc_to_msg(v, a);
     B::set_flags(v, flag);
 #pragma unroll
@@ -256,12 +274,12 @@ B200_HD void run_sequential(const Ctx<B>& c, int wire) {
     B::restore(v);
     B::store(c.out, int64_t(r) * p.chunk_dw + off, chunk_end(r), p.odd_dw, v);
 #pragma unroll
-    for (int i = 0; i < N; ++i) src[i] = txn_at<B>(c.sink(1), idx(from[i]));
-    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 1, from, t)) return;
-#pragma unroll
     for (int i = 1; i < N; ++i) {
-      B::restore(m[i]);
-      B::store(c.out, int64_t(from[i]) * p.chunk_dw + off, chunk_end(from[i]), p.odd_dw, m[i]);
+      const int q = (r + i) % N;
+      typename B::Msg m;
+      B200_WAIT(c, m, txn_at<B>(c.sink(1), idx(q)), flag, 1, q, t);
+      B::restore(m);
+      B::store(c.out, int64_t(q) * p.chunk_dw + off, chunk_end(q), p.odd_dw, m);
     }
   }
 }
@@ -406,20 +424,16 @@ B200_HD void run_direct_allgather(const Ctx<B>& c, int wire) {
       const int q = (r + i) % N;
       c.send(txn_at<B>(c.peer_sink(1, q), idx(r)), v);
     }
-    typename B::Msg m[N];
-    const char* src[N];
-    int from[N];
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-      from[i] = (r + i) % N;
-      src[i] = txn_at<B>(c.sink(1), idx(from[i]));
-    }
-    if (!c.wait_many(m, src, (1u << N) - 2u, flag, 1, from, t)) return;
-#pragma unroll
-    for (int i = 1; i < N; ++i) {
-      B::restore(m[i]);
-      B::store(c.out, int64_t(from[i]) * shard_dw + off, int64_t(from[i] + 1) * shard_dw, -1, m[i]);
-    }
+    if (!recv_in_order<B, 1, N>(
+            c, flag, 1, t, -1, v, [&](int i) -> const char* { return txn_at<B>(c.sink(1), idx((r + i) % N)); },
+            [&](int i) { return (r + i) % N; },
+            [&](int i, const typename B::Msg& x) {
+              const int q = (r + i) % N;
+              typename B::Msg y = x;
+              B::restore(y);
+              B::store(c.out, int64_t(q) * shard_dw + off, int64_t(q + 1) * shard_dw, -1, y);
+            }))
+      return;
   }
 }
 
@@ -481,18 +495,14 @@ B200_HD void run_bisect(const Ctx<B>& c, int wire) {
       B200_WAIT(c, v, txn_at<B>(c.sink(1), (int64_t(g) * BI + y) * kParallelSlots + slot), flag, 1,
                 2 * y + parity, t);
     } else {
-      typename B::Msg m[BI];
-      const char* src[BI];
-      int from[BI];
-#pragma unroll
-      for (int i = 0; i < BI; ++i) {
-        const int ql = (l + i) % BI;
-        from[i] = 2 * ql + parity;
-        src[i] = txn_at<B>(c.sink(0), (int64_t(g) * BI + ql) * kParallelSlots + slot);
-      }
-      if (BI > 1 && !c.wait_many(m, src, (1u << BI) - 2u, flag, 0, from, t)) return;
-#pragma unroll
-      for (int i = 1; i < BI; ++i) B::acc_add(a, m[i], c.round_each());
+      if (!recv_in_order<B, 1, BI>(
+              c, flag, 0, t, -1, v,
+              [&](int i) -> const char* {
+                return txn_at<B>(c.sink(0), (int64_t(g) * BI + (l + i) % BI) * kParallelSlots + slot);
+              },
+              [&](int i) { return 2 * ((l + i) % BI) + parity; },
+              [&](int, const typename B::Msg& x) { B::acc_add(a, x, c.round_each()); }))
+        return;
       B::acc_to_msg(v, a);
       B::set_flags(v, flag);
 #pragma unroll
@@ -544,23 +554,16 @@ B200_HD void run_oneshot(const Ctx<B>& c, int wire) {
       const int q = (r + i) % N;
       c.send(at(c.peer_oneshot(q), r), v);
     }
-    // all world - 1 landing slots are polled together; m[q] is rank q's slice, own slice at m[r]
+    // the world - 1 landing slots are polled in overlapping groups; slices are added in rank order,
+    // the own one (its flag dwords differ from a received copy, but no accumulator slot reads them) at r
     typename B::Acc a;
-    typename B::Msg m[N];
-    const char* src[N];
-    int from[N];
-#pragma unroll
-    for (int q = 0; q < N; ++q) {
-      from[q] = q;
-      src[q] = at(c.oneshot(), q);
-    }
-    if (!c.wait_many(m, src, ((1u << N) - 1u) & ~(1u << r), flag, 4, from, t)) return;
-#pragma unroll
-    for (int q = 0; q < N; ++q) {
-      if (q == r) m[q] = v;  // flag dwords differ from a received copy, but no accumulator slot reads them
-      if (q == 0) B::acc_init(a, m[q]);
-      else B::acc_add(a, m[q], c.round_each());
-    }
+    if (!recv_in_order<B, 0, N>(
+            c, flag, 4, t, r, v, [&](int q) -> const char* { return at(c.oneshot(), q); }, [&](int q) { return q; },
+            [&](int q, const typename B::Msg& x) {
+              if (q == 0) B::acc_init(a, x);
+              else B::acc_add(a, x, c.round_each());
+            }))
+      return;
     B::acc_to_msg(v, a);
     B::restore(v);
     B::store(c.out, dw, total_dw, odd_dw, v);

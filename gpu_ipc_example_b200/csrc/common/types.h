@@ -83,6 +83,7 @@ struct HeapLayout {
 
 // Offsets inside the control region.
 constexpr size_t kCtrlAbortOff = 0;            // uint32 abort word
+constexpr size_t kCtrlClaimOff = 4;            // uint32: which wire writes this rank's status record (0 = nobody yet)
 constexpr size_t kCtrlSeqOff = 256;            // uint32 {sequence offset, finished-CTA counter, barrier offset, -}
 constexpr size_t kCtrlBarrierOff = 4096;       // uint32 pad[kMaxBarrierCtas][kMaxRanks]
 constexpr int kMaxBarrierCtas = 1024;

@@ -113,11 +113,11 @@ struct HostBackend : WireFormat<K> {
   }
 
   // Several transactions at once (see DevBackend::wait_many); a scalar rank has nothing to overlap.
-  template <int CNT>
-  static bool wait_many(const HostWaiter& w, Msg (&m)[CNT], const char* const (&src)[CNT], uint32_t pending, uint32_t flag,
-                        int site, const int (&peer)[CNT], int64_t step, int rank) {
+  template <int CNT, class SrcFn, class PeerFn>
+  static bool wait_many(const HostWaiter& w, Msg (&m)[CNT], SrcFn src, PeerFn peer, uint32_t pending, uint32_t flag, int site,
+                        int64_t step, int rank) {
     for (int i = 0; i < CNT; ++i)
-      if ((pending & (1u << i)) && !wait(w, m[i], src[i], flag, site, peer[i], step, rank)) return false;
+      if ((pending & (1u << i)) && !wait(w, m[i], src(i), flag, site, peer(i), step, rank)) return false;
     return true;
   }
 

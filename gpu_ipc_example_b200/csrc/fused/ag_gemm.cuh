@@ -125,14 +125,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
             if (int32_t(seen - args.arrive_target) >= 0) break;
             if ((++spins & 0x3fu) == 0) {
               if (ld_volatile_u32(abort_word) != 0) {
-                note_aborted_by_peer(me.status, rank, 30);
+                note_aborted_by_peer(abort_word, me.status, rank, 30);
                 ok = false;
                 break;
               }
               const uint64_t now = globaltimer_ns();
               if (t0 == 0) t0 = now;
               else if (now - t0 > me.timeout_ns) {
-                if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+                if (claim_status(abort_word, kTimeout)) {
                   StatusBlock* sb = me.status;
                   sb->rank = uint32_t(rank);
                   sb->peer = uint32_t(q);
@@ -144,8 +144,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
                   sb->code = kTimeout;
                   __threadfence_system();
                 }
-                for (int p = 0; p < W; ++p)
-                  if (p != rank) st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[p] + lay.ctrl_off + kCtrlAbortOff), 1u);
+                for (int p = 0; p < W; ++p)  // own abort word included
+                  st_volatile_u32(reinterpret_cast<uint32_t*>(me.peer[p] + lay.ctrl_off + kCtrlAbortOff), 1u);
                 ok = false;
                 break;
               }
@@ -253,7 +253,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (*abort_flag && threadIdx.x == 0) {
     uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
-    if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+    st_volatile_u32(abort_word, 1u);
+    if (claim_status(abort_word, kTimeout)) {
       StatusBlock* sb = me.status;
       sb->rank = uint32_t(rank);
       sb->peer = uint32_t(rank);

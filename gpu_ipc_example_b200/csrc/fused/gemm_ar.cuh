@@ -211,7 +211,7 @@ struct RowCtx {
         if (seen == seq) break;
         if ((++spins & 0x3fu) == 0) {
           if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
-            if (ld_volatile_u32(abort_word) != 0) note_aborted_by_peer(me->status, me->rank, 21);
+            if (ld_volatile_u32(abort_word) != 0) note_aborted_by_peer(abort_word, me->status, me->rank, 21);
             *fail = 1;
             ok = false;
             break;
@@ -219,7 +219,7 @@ struct RowCtx {
           const uint64_t now = globaltimer_ns();
           if (t0 == 0) t0 = now;
           else if (now - t0 > me->timeout_ns) {
-            if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+            if (claim_status(abort_word, kTimeout)) {
               StatusBlock* sb = me->status;
               sb->rank = uint32_t(me->rank);
               sb->peer = uint32_t(src);
@@ -232,8 +232,8 @@ struct RowCtx {
               sb->code = kTimeout;
               __threadfence_system();
             }
-            for (int q = 0; q < W; ++q)
-              if (q != me->rank) st_volatile_u32(reinterpret_cast<uint32_t*>(me->peer[q] + lay->ctrl_off + kCtrlAbortOff), 1u);
+            for (int q = 0; q < W; ++q)  // own abort word included
+              st_volatile_u32(reinterpret_cast<uint32_t*>(me->peer[q] + lay->ctrl_off + kCtrlAbortOff), 1u);
             *fail = 1;
             ok = false;
             break;
@@ -535,7 +535,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   if (*abort_flag) {
     if (threadIdx.x == 0) {
       uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
-      if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+      st_volatile_u32(abort_word, 1u);
+      if (claim_status(abort_word, kTimeout)) {
         StatusBlock* sb = me.status;
         sb->rank = uint32_t(rank);
         sb->peer = uint32_t(rank);
@@ -614,13 +615,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       if (int32_t(seen - done_target) >= 0) break;
       if ((++spins & 0x3fu) == 0) {
         if (ld_volatile_u32(abort_word) != 0) {
-          note_aborted_by_peer(me.status, rank, 22);
+          note_aborted_by_peer(abort_word, me.status, rank, 22);
           break;
         }
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) t0 = now;
         else if (now - t0 > me.timeout_ns) {
-          if (atomicCAS(abort_word, 0u, 1u) == 0u) {
+          st_volatile_u32(abort_word, 1u);
+          if (claim_status(abort_word, kTimeout)) {
             StatusBlock* sb = me.status;
             sb->rank = uint32_t(rank);
             sb->peer = 0;

@@ -104,25 +104,20 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
         }
       }
     }
-    // all world - 1 landing slots are polled together (a poll is a round trip to L2)
+    // the world - 1 landing slots are polled in overlapping groups (a poll is a round trip to L2);
+    // slices are added in rank order, the own one at position r
     typename B::Acc a;
-    typename B::Msg m[N];
-    if (N > 1) {
-      const char* src[N];
-      int from[N];
-#pragma unroll
-      for (int q = 0; q < N; ++q) {
-        from[q] = q;
-        src[q] = at(me.heap, q);
-      }
-      ok = B::template wait_many<N>(waiter, m, src, ((1u << N) - 1u) & ~(1u << r), flag, 5, from, k, r);
+    {
+      Ctx<B> cx{};
+      cx.waiter = waiter;
+      cx.rank = r;
+      ok = recv_in_order<B, 0, N>(
+          cx, flag, 5, k, r, v, [&](int q) -> const char* { return at(me.heap, q); }, [&](int q) { return q; },
+          [&](int q, const typename B::Msg& x) {
+            if (q == 0) B::acc_init(a, x);
+            else B::acc_add(a, x, false);
+          });
       if (!ok) break;
-    }
-#pragma unroll
-    for (int q = 0; q < N; ++q) {
-      if (q == r) m[q] = v;
-      if (q == 0) B::acc_init(a, m[q]);
-      else B::acc_add(a, m[q], false);
     }
 
     if (EPI == kEpiNorm) {

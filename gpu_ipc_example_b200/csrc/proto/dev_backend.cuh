@@ -53,17 +53,21 @@ __device__ __forceinline__ void st_volatile_v4(void* p, const uint32_t (&d)[4]) 
                : "memory");
 }
 
-// A wait that gave up because ANOTHER wire or rank raised the abort word: leave a trace in this
-// rank's status block (pinned host memory) unless a more specific record is already there, so that
-// the host's check raises on every rank of an aborted collective, not only on the one that timed out.
-__device__ __forceinline__ void note_aborted_by_peer(StatusBlock* s, int rank, int site) {
-  if (ld_volatile_u32(&s->code) == kOk) {
-    s->rank = uint32_t(rank);
-    s->where = uint32_t(site);
-    __threadfence_system();
-    s->code = kAbortedByPeer;
-    __threadfence_system();
-  }
+// One wire per rank writes the rank's status record (pinned host memory): the first that has
+// something to report claims it, either as "my wait ran out" (kTimeout) or as "I was told to
+// stop" (kAbortedByPeer).  With a single writer a record is never half one and half the other,
+// and the host's check raises on every rank of an aborted collective, not only on the one whose
+// wait ran out.  `abort_word` is the rank's own abort word; the claim word sits next to it.
+__device__ __forceinline__ bool claim_status(uint32_t* abort_word, uint32_t kind) {
+  return atomicCAS(abort_word + (kCtrlClaimOff - kCtrlAbortOff) / 4, 0u, kind) == 0u;
+}
+__device__ __forceinline__ void note_aborted_by_peer(uint32_t* abort_word, StatusBlock* s, int rank, int site) {
+  if (!claim_status(abort_word, kAbortedByPeer)) return;
+  s->rank = uint32_t(rank);
+  s->where = uint32_t(site);
+  __threadfence_system();
+  s->code = kAbortedByPeer;
+  __threadfence_system();
 }
 
 struct DevWaiter {
@@ -282,17 +286,17 @@ struct DevBackend : WireFormat<K> {
   }
 
   // Waits for several transactions at once: bit i of `pending` set = m[i] is still expected from
-  // src[i] (sent by rank peer[i]).  Every round issues the loads of all pending transactions
+  // src(i) (sent by rank peer(i)).  Every round issues the loads of all pending transactions
   // back to back and only then tests them, so the round trips overlap instead of adding up.
-  template <int CNT>
-  __device__ static bool wait_many(const DevWaiter& w, Msg (&m)[CNT], const char* const (&src)[CNT], uint32_t pending,
-                                   uint32_t flag, int site, const int (&peer)[CNT], int64_t step, int rank) {
+  template <int CNT, class SrcFn, class PeerFn>
+  __device__ static bool wait_many(const DevWaiter& w, Msg (&m)[CNT], SrcFn src, PeerFn peer, uint32_t pending,
+                                   uint32_t flag, int site, int64_t step, int rank) {
     uint32_t spins = 0;
     uint64_t t0 = 0;
     for (;;) {
 #pragma unroll
       for (int i = 0; i < CNT; ++i)
-        if (pending & (1u << i)) recv_load(m[i], src[i]);
+        if (pending & (1u << i)) recv_load(m[i], src(i));
       uint32_t mine = 0;
 #pragma unroll
       for (int i = 0; i < CNT; ++i)
@@ -316,16 +320,8 @@ struct DevBackend : WireFormat<K> {
         give_up = __shfl_sync(0xffffffffu, give_up, 0);
         if (give_up) {
           const int first = __ffs(int(pending)) - 1;
-          int who = peer[0];
-          const char* where = src[0];
-#pragma unroll
-          for (int i = 1; i < CNT; ++i)
-            if (i == first) {
-              who = peer[i];
-              where = src[i];
-            }
-          if (give_up == 2) report_timeout(w, where, flag, site, who, step, rank);
-          else if (lane() == 0) note_aborted_by_peer(w.me->status, rank, site);
+          if (give_up == 2) report_timeout(w, src(first), flag, site, peer(first), step, rank);
+          else if (lane() == 0) note_aborted_by_peer(w.abort_word(), w.me->status, rank, site);
           return false;
         }
       }
@@ -355,7 +351,7 @@ struct DevBackend : WireFormat<K> {
         give_up = __shfl_sync(0xffffffffu, give_up, 0);
         if (give_up) {
           if (give_up == 2) report_timeout(w, src, flag, site, peer, step, rank);
-          else if (lane() == 0) note_aborted_by_peer(w.me->status, rank, site);
+          else if (lane() == 0) note_aborted_by_peer(w.abort_word(), w.me->status, rank, site);
           return false;
         }
       }
@@ -367,7 +363,7 @@ struct DevBackend : WireFormat<K> {
     const int l = lane();
     if (l == 0) {
       StatusBlock* s = w.me->status;
-      if (atomicCAS(reinterpret_cast<unsigned int*>(w.abort_word()), 0u, 1u) == 0u) {
+      if (claim_status(w.abort_word(), kTimeout)) {
         // first wire of this rank to give up: record the site
         s->rank = uint32_t(rank);
         s->peer = uint32_t(peer);
@@ -380,6 +376,7 @@ struct DevBackend : WireFormat<K> {
         s->code = kTimeout;
       }
       __threadfence_system();
+      st_volatile_u32(w.abort_word(), 1u);
     }
     if (l < w.me->world && l != rank) st_volatile_u32(w.peer_abort(l), 1u);
   }
