@@ -154,6 +154,14 @@ class Comm {
     *parity = int(ag_launches_++ & 1u);
     return ag_arrive_;
   }
+  // Launch number of the fused GEMM kernels (flag value; its parity picks the half of the one-shot
+  // landing zone).  Never reset: a stale flag must not equal a later launch's number.
+  uint32_t take_gemm_epoch() {
+    if (device_seq_) return gemm_epoch_ + 1;  // the device adds its own running offset
+    ++gemm_epoch_;
+    if (gemm_epoch_ == 0) gemm_epoch_ = 1;
+    return gemm_epoch_;
+  }
   void reset_fused_counters() {
     gemm_done_ = 0;
     ag_arrive_ = 0;
@@ -176,6 +184,7 @@ class Comm {
   uint32_t seq_ = 1;
   uint32_t bar_seq_ = 0;
   uint32_t gemm_done_ = 0;
+  uint32_t gemm_epoch_ = 0;
   uint32_t ag_arrive_ = 0;
   uint32_t ag_launches_ = 0;
   bool device_seq_ = false;

@@ -45,8 +45,12 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
       {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
       {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {16 * MiB, SchedKind::Parallel, ProtoKind::LL512},
       {0, SchedKind::Bulk, ProtoKind::LL512}};
-  static const TuneRow w2[] = {
-      {64 * KiB, SchedKind::OneShot, ProtoKind::LL512},    {2 * MiB, SchedKind::Parallel, ProtoKind::LL512},
+  // two ranks: one hop moves as many bytes as two, so the one-shot schedule reaches far
+  static const TuneRow w2_sym[] = {
+      {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {2 * MiB, SchedKind::Sequential, ProtoKind::LL512},
+      {0, SchedKind::Bulk, ProtoKind::LL512}};
+  static const TuneRow w2_user[] = {
+      {4 * MiB, SchedKind::OneShot, ProtoKind::LL512},     {16 * MiB, SchedKind::Ring, ProtoKind::LL512},
       {0, SchedKind::Bulk, ProtoKind::LL512}};
   if (world >= 8) {
     *rows = symmetric ? 6 : 7;
@@ -57,7 +61,7 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
     return symmetric ? w4_sym : w4_user;
   }
   *rows = 3;
-  return w2;
+  return symmetric ? w2_sym : w2_user;
 }
 
 }  // namespace b200ipc

@@ -37,7 +37,7 @@ constexpr size_t kAgCounterOff = kCtrlSeqOff + 64;  // uint32 arrived[kMaxRanks]
 template <typename T, int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_constant__ AgGemmArgs args) {
   extern __shared__ unsigned char smem_raw[];
-  using Smem = GemmSmem<BN, STAGES>;
+  using Smem = GemmSmem<BN, STAGES, kGemmBM>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const RankView& me = args.k.v[blockIdx.y];
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int st = int(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag)) break;
+          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, me.timeout_ns)) break;
           mbar_expect_tx(&s.full[st], kStageBytes);
           tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
           tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
       }
       for (uint32_t back = 0; back < uint32_t(STAGES) && back < it; ++back) {
         const uint32_t j = it - 1 - back;
-        mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1u, abort_flag);
+        mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1u, abort_flag, me.timeout_ns);
       }
     }
   } else if (warp == 1) {
@@ -180,14 +180,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
       for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
         const uint32_t buf = tile_i & 1u;
         const uint32_t use = tile_i >> 1;
-        if (!mbar_wait(&s.acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(&s.acc_empty[buf], (use & 1u) ^ 1u, abort_flag, me.timeout_ns)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         bool ok = true;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int st = int(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&s.full[st], ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&s.full[st], ph, abort_flag, me.timeout_ns)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st]));
           const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st]));
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
       const int mt = (t / n_tiles + first_mt) % m_tiles, nt = t % n_tiles;
       const uint32_t buf = tile_i & 1u;
       const uint32_t use = tile_i >> 1;
-      if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag)) break;
+      if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag, me.timeout_ns)) break;
       tc_fence_after_sync();
 #pragma unroll 1
       for (int c = 0; c < BN; c += 64) {

@@ -40,9 +40,10 @@ struct GemmArPtrs {
   void* workspace;       // gemm_ar_workspace() bytes in the symmetric heap, zeroed once before first use
 };
 struct GemmArWorkspace {
-  size_t landing_bytes = 0;
-  size_t flags_bytes = 0;
-  size_t total() const { return landing_bytes + flags_bytes; }
+  size_t landing_bytes = 0;  // partial products landing here
+  size_t flags_bytes = 0;    // one flag per (source, tile, row group)
+  size_t inv_bytes = 0;      // 1/rms of every row, written by the row's owner
+  size_t total() const { return landing_bytes + flags_bytes + inv_bytes; }
 };
 GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N);
 CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,

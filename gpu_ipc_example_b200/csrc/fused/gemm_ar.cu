@@ -1,5 +1,7 @@
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <mutex>
 #include <set>
@@ -14,20 +16,25 @@
 namespace b200ipc {
 namespace {
 
-constexpr int kStages256 = 4;  // 4 x (16 KiB + 32 KiB) = 192 KiB of the 227 KiB a CTA may use
-constexpr int kStages128 = 6;  // 6 x (16 KiB + 16 KiB) = 192 KiB
-constexpr int kStages64 = 8;   // 8 x (16 KiB +  8 KiB) = 192 KiB
+constexpr int kStages256 = 4;   // 4 x (16 KiB + 32 KiB) = 192 KiB of the 227 KiB a CTA may use
+constexpr int kStages128 = 6;   // 6 x (16 KiB + 16 KiB) = 192 KiB
+constexpr int kStages64 = 8;    // 8 x (16 KiB +  8 KiB) = 192 KiB
+constexpr int kStagesDecode = 16;  // 16 x (4 KiB + 8 KiB) = 192 KiB: M <= 32, the X stage holds 32 rows
+constexpr int kDecodeRows = 32;
 
-template <typename T, int BN, int STAGES>
+template <typename T, int BN, int STAGES, int A_ROWS>
 const void* kernel_ptr() {
-  return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES>);
+  return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES, A_ROWS>);
 }
 
 // Tensor maps depend only on (pointer, extents, box, type): weights and activation buffers are
-// reused call after call, so encoding is done once per distinct operand.
+// reused call after call, so encoding is done once per distinct operand.  The cache is bounded: when
+// it is full the oldest entry makes room (never a wholesale clear in the middle of serving).
 using MapKey = std::tuple<const void*, uint64_t, uint64_t, uint32_t, int>;
+constexpr size_t kMaxCachedMaps = 4096;
 std::mutex g_map_mu;
 std::map<MapKey, CUtensorMap> g_maps;
+std::deque<MapKey> g_map_order;
 std::set<const void*> g_attr_done;
 
 void encode_2d(CUtensorMap* map, DType t, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
@@ -51,8 +58,26 @@ void encode_2d(CUtensorMap* map, DType t, const void* base, uint64_t rows, uint6
                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   std::lock_guard<std::mutex> lk(g_map_mu);
-  if (g_maps.size() > 4096) g_maps.clear();
-  g_maps[key] = *map;
+  if (g_maps.emplace(key, *map).second) {
+    g_map_order.push_back(key);
+    if (g_map_order.size() > kMaxCachedMaps) {
+      g_maps.erase(g_map_order.front());
+      g_map_order.pop_front();
+    }
+  }
+}
+
+size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+// Which exchange a problem uses: one-shot for decode-sized M (every rank gets every partial, one NVLink
+// hop), reduce-scatter + all-gather otherwise.  B200IPC_GEMM_MODE=rs|oneshot overrides (oneshot only
+// where M allows it).
+int gemm_mode_for(int64_t M) {
+  int mode = M <= kGemmOneShotMaxRows ? kGemmModeOneShot : kGemmModeReduceScatter;
+  if (const char* e = std::getenv("B200IPC_GEMM_MODE")) {
+    if (std::strcmp(e, "rs") == 0) mode = kGemmModeReduceScatter;
+  }
+  return mode;
 }
 
 }  // namespace
@@ -61,10 +86,14 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
   GemmArWorkspace w;
   const int64_t rpr = (M + world - 1) / world;
   const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
-  w.landing_bytes = size_t(world) * size_t(rpr) * size_t(N) * 2;
-  w.landing_bytes = (w.landing_bytes + 255) / 256 * 256;
-  w.flags_bytes = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
-  w.flags_bytes = (w.flags_bytes + 255) / 256 * 256;
+  // room for either form of the exchange, so that the choice can change between calls
+  const size_t rs_landing = size_t(world) * size_t(rpr) * size_t(N) * 2;
+  const size_t os_landing = M <= kGemmOneShotMaxRows ? 2 * up256(size_t(world) * size_t(M) * size_t(N) * 2) : 0;
+  w.landing_bytes = up256(std::max(rs_landing, os_landing));
+  const size_t rs_flags = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
+  const size_t os_flags = 2 * size_t(world) * size_t(N / 64) * sizeof(uint32_t);
+  w.flags_bytes = up256(std::max(rs_flags, os_flags));
+  w.inv_bytes = up256(size_t(M) * sizeof(float));
   return w;
 }
 
@@ -76,21 +105,26 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   B200_REQUIRE(K % 8 == 0, "K must be a multiple of 8");
   B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
+  const int mode = gemm_mode_for(M);
   // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
   // cut the operand traffic per FLOP for large M.
   const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  const bool decode = BN == 64 && M <= kDecodeRows;  // short X stage, deep ring
   const void* fn;
   size_t smem;
   const bool h = t == DType::F16;
-  if (BN == 64) {
-    fn = h ? kernel_ptr<__half, 64, kStages64>() : kernel_ptr<__nv_bfloat16, 64, kStages64>();
-    smem = sizeof(GemmSmem<64, kStages64>) + 1024;
+  if (decode) {
+    fn = h ? kernel_ptr<__half, 64, kStagesDecode, kDecodeRows>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode, kDecodeRows>();
+    smem = sizeof(GemmSmem<64, kStagesDecode, kDecodeRows>) + 1024;
+  } else if (BN == 64) {
+    fn = h ? kernel_ptr<__half, 64, kStages64, kGemmBM>() : kernel_ptr<__nv_bfloat16, 64, kStages64, kGemmBM>();
+    smem = sizeof(GemmSmem<64, kStages64, kGemmBM>) + 1024;
   } else if (BN == 128) {
-    fn = h ? kernel_ptr<__half, 128, kStages128>() : kernel_ptr<__nv_bfloat16, 128, kStages128>();
-    smem = sizeof(GemmSmem<128, kStages128>) + 1024;
+    fn = h ? kernel_ptr<__half, 128, kStages128, kGemmBM>() : kernel_ptr<__nv_bfloat16, 128, kStages128, kGemmBM>();
+    smem = sizeof(GemmSmem<128, kStages128, kGemmBM>) + 1024;
   } else {
-    fn = h ? kernel_ptr<__half, 256, kStages256>() : kernel_ptr<__nv_bfloat16, 256, kStages256>();
-    smem = sizeof(GemmSmem<256, kStages256>) + 1024;
+    fn = h ? kernel_ptr<__half, 256, kStages256, kGemmBM>() : kernel_ptr<__nv_bfloat16, 256, kStages256, kGemmBM>();
+    smem = sizeof(GemmSmem<256, kStages256, kGemmBM>) + 1024;
   }
   {
     std::lock_guard<std::mutex> lk(g_map_mu);
@@ -106,7 +140,9 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   const int64_t total_tiles = m_tiles * n_tiles;
   int cap = comm.resident_ctas(reinterpret_cast<KernelFn>(const_cast<void*>(fn)), kGemmThreads, smem);
   B200_REQUIRE(cap >= 1, "GEMM kernel does not fit on the device");
-  int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, std::max<int64_t>(total_tiles, std::min<int64_t>(rpr, cap))));
+  // enough CTAs for the tiles, and for the rows of the phase that follows (one row per CTA at a time)
+  const int64_t rows_after = mode == kGemmModeOneShot ? M : rpr;
+  int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, std::max<int64_t>(total_tiles, std::min<int64_t>(rows_after, cap))));
   B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs, only " << cap << " can run at once");
 
   int a_box = kGemmBM;
@@ -117,6 +153,7 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   GemmArArgs args;
   std::memset(&args, 0, sizeof(args));
   args.a_box_rows = a_box;
+  args.mode = mode;
   std::vector<const void*> ins(size_t(comm.nlocal()), nullptr);
   std::vector<void*> outs(size_t(comm.nlocal()), nullptr);
   comm.fill_views(&args.k, ins.data(), outs.data(), size_t(M * N), 0);
@@ -150,27 +187,27 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   args.with_norm = with_norm ? 1 : 0;
   args.landing_off = landing_off;
   args.flags_off = landing_off + ws.landing_bytes;
+  args.inv_off = args.flags_off + ws.flags_bytes;
   args.out_off = out_off;
   args.res_out_off = res_off;
-  const uint32_t first = comm.take_seq(2);
-  const uint32_t deliveries = uint32_t(W) * uint32_t(ctas);
-  args.done_target = comm.device_seq() ? deliveries : comm.take_done(deliveries);
-  for (int i = 0; i < comm.nlocal(); ++i) {
-    args.k.v[i].seq = first;
-    args.k.v[i].seq_step = 2;
+  args.oneshot_half_bytes = up256(size_t(W) * size_t(M) * size_t(N) * 2);
+  args.epoch = comm.take_gemm_epoch();
+  if (mode == kGemmModeReduceScatter) {
+    const uint32_t deliveries = uint32_t(W) * uint32_t(ctas);
+    args.done_target = comm.device_seq() ? deliveries : comm.take_done(deliveries);
   }
 
   void* params[] = {&args};
   comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
 
   CollInfo info;
-  info.sched = SchedKind::Bulk;
+  info.sched = mode == kGemmModeOneShot ? SchedKind::OneShot : SchedKind::Bulk;
   info.proto = ProtoKind::LL512;
   info.ctas = ctas;
   info.warps = kGemmThreads / 32;
   info.nwires = ctas * kGemmThreads / 32;
   info.steps = (total_tiles + ctas - 1) / ctas;
-  info.first_flag = first;
+  info.first_flag = args.epoch;
   info.launches = 1;
   return info;
 }
@@ -196,13 +233,13 @@ CollInfo fused_allgather_gemm(Comm& comm, DType t, const AgGemmPtrs* ptrs, int64
   const bool h = t == DType::F16;
   if (BN == 64) {
     fn = h ? ag_kernel_ptr<__half, 64, kStages64>() : ag_kernel_ptr<__nv_bfloat16, 64, kStages64>();
-    smem = sizeof(GemmSmem<64, kStages64>) + 1024;
+    smem = sizeof(GemmSmem<64, kStages64, kGemmBM>) + 1024;
   } else if (BN == 128) {
     fn = h ? ag_kernel_ptr<__half, 128, kStages128>() : ag_kernel_ptr<__nv_bfloat16, 128, kStages128>();
-    smem = sizeof(GemmSmem<128, kStages128>) + 1024;
+    smem = sizeof(GemmSmem<128, kStages128, kGemmBM>) + 1024;
   } else {
     fn = h ? ag_kernel_ptr<__half, 256, kStages256>() : ag_kernel_ptr<__nv_bfloat16, 256, kStages256>();
-    smem = sizeof(GemmSmem<256, kStages256>) + 1024;
+    smem = sizeof(GemmSmem<256, kStages256, kGemmBM>) + 1024;
   }
   {
     std::lock_guard<std::mutex> lk(g_map_mu);

@@ -3,24 +3,33 @@
 //     Y = sum over ranks r of  X_r[M, K] . W_r[N, K]^T          (each rank holds a K-slice)
 //     res_out = Y + residual ;  out = RMSNorm(res_out) * gamma   (or out = Y without the norm)
 //
-// in ONE kernel per rank:
-//   1. GEMM on the 5th-generation tensor cores: TMA (cp.async.bulk.tensor, 128-byte
-//      swizzle, no multicast) streams 128 x 64 tiles of X and BN x 64 tiles of W into a
-//      shared-memory ring; one elected thread issues tcgen05.mma (M = 128, N = BN, K = 16)
-//      into a double-buffered fp32 accumulator in tensor memory; four epilogue warps read
-//      it back with tcgen05.ld.
-//   2. Reduce-scatter inside the epilogue: each finished tile is rounded to 16 bit and
-//      stored straight into the memory of the rank that owns those rows (peer stores over
-//      NVLink), then one flag per (source, tile) is released - so the transfer of tile i
-//      overlaps the math of tile i+1.
-//   3. The owner adds the world partial copies of its rows in rank order in fp32, adds the
-//      residual, computes the row statistic, and pushes the normalised rows and the new
-//      residual to every rank (all-gather), again with plain peer stores.
-//   4. A counter per rank tells when every owner has delivered; the kernel ends only then.
-// Rows are owned in contiguous blocks of ceil(M / world).  Every wait is bounded; the
-// waits on peers come after tensor memory has been returned.
+// in ONE kernel per rank.  The GEMM runs on the 5th-generation tensor cores: TMA
+// (cp.async.bulk.tensor, 128-byte swizzle, no multicast) streams tiles of X and BN x 64 tiles
+// of W into a shared-memory ring; one elected thread issues tcgen05.mma (M = 128, N = BN,
+// K = 16) into a double-buffered fp32 accumulator in tensor memory; four epilogue warps read
+// it back with tcgen05.ld.  The exchange comes in two forms:
 //
-// No counterpart in the reference.  Baseline: cuBLAS GEMM + NCCL all-reduce + a separate
+//   reduce-scatter (any M):  the epilogue rounds each finished tile to 16 bit and stores it
+//     straight into the memory of the rank that OWNS those rows (peer stores over NVLink), then
+//     releases one flag per (source, tile, 32-row group) - the transfer of tile i overlaps the
+//     math of tile i+1.  Six more warps of every CTA are the owner side and run AT THE SAME
+//     TIME as the GEMM: they wait for the flags of an owned row, add the world partial copies
+//     in rank order in fp32 (+ residual), and push the summed row and its 1/rms to every rank
+//     (all-gather by peer stores).  Tiles are visited so that every owner's rows complete at an
+//     even pace.  A delivery counter per rank tells when all owners are done; then every rank
+//     normalises the rows locally (out = sum * 1/rms * gamma), so only ONE tensor crosses the
+//     links in the all-gather.
+//   one-shot (M <= 32, decode):  the epilogue stores each finished tile into EVERY rank (one
+//     NVLink hop, no owner, no all-gather); each rank adds the world copies of a row, the
+//     residual, and normalises.  Landing zone and flags alternate between two halves by launch
+//     parity: a rank can be at most one launch ahead of a peer, so it never overwrites rows a
+//     peer still reads.
+//
+// Small M is a weight-streaming problem: the X stage of the ring shrinks to the rows that
+// exist, which buys a ring deep enough (16 stages) to keep HBM busy.
+// Every wait is bounded (time limit of the communicator); tensor memory is always returned.
+//
+// No counterpart in the reference.  Baseline: cuBLAS GEMM + NCCL all-reduce + a fused
 // add/normalise kernel.
 #pragma once
 
@@ -33,9 +42,12 @@ namespace b200ipc {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;        // 64 x 2 B = one 128-byte swizzle row
-constexpr int kGemmThreads = 384;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue; warps 6-11 only
-                                   // join the memory-bound owner phase, which wants many loads in flight
-constexpr uint32_t kMbarSpinLimit = 1u << 24;
+constexpr int kGemmThreads = 384;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-11: owner side
+constexpr int kGemmOwnerWarps = 6;
+constexpr int kGemmOwnerThreads = kGemmOwnerWarps * 32;
+constexpr int kGemmModeReduceScatter = 0;
+constexpr int kGemmModeOneShot = 1;
+constexpr int kGemmOneShotMaxRows = 32;
 
 struct GemmArArgs {
   KArgs k;
@@ -46,15 +58,20 @@ struct GemmArArgs {
   int M, N, K;
   int rows_per_rank;
   int a_box_rows;        // rows of X one TMA box brings in: 128, or fewer when M is small (the rest of the
-                         // 128-row operand tile then holds stale data, which only reaches accumulator rows >= M)
-  uint32_t done_target;  // value the local delivery counter reaches when all owners are done
+                         // 128-row operand tile then holds other data, which only reaches accumulator rows >= M)
+  int mode;              // kGemmModeReduceScatter / kGemmModeOneShot
+  uint32_t done_target;  // value the local delivery counter reaches when all owners are done (reduce-scatter)
+  uint32_t epoch;        // launch number of this kernel family on the communicator: flag value, and its parity
+                         // picks the half of the one-shot landing zone
   float eps;
   int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
   // heap offsets (same on every rank)
-  uint64_t landing_off;  // [world][rows_per_rank][N] 16-bit partials
-  uint64_t flags_off;    // [world][m_tiles][n_tiles] uint32
+  uint64_t landing_off;  // reduce-scatter: [world][rows_per_rank][N]; one-shot: [2][world][M][N]   16-bit partials
+  uint64_t flags_off;    // reduce-scatter: [world][m_tiles][n_tiles][4]; one-shot: [2][world][n_tiles]   uint32
+  uint64_t inv_off;      // [M] fp32: 1/rms of every row, written by the row's owner
   uint64_t out_off;      // [M][N]
   uint64_t res_out_off;  // [M][N] (0 = not wanted)
+  uint64_t oneshot_half_bytes;  // size of one half of the one-shot landing zone
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -80,11 +97,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up (and tells the whole CTA through *abort_flag) after kMbarSpinLimit polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t n = 0; n < kMbarSpinLimit; ++n) {
+// Bounded wait: gives up (and tells the whole CTA through *abort_flag) when the communicator's time
+// limit for one wait has passed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t timeout_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t n = 0;; ++n) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((n & 1023u) == 1023u && *abort_flag) return false;
+    if ((n & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) break;
+    }
   }
   *abort_flag = 1;
   return false;
@@ -158,7 +182,7 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
 
 // Phase time stamps of CTA 0 (global timer, ns), kept in the control region of the heap at
 // kGemmTraceOff: [0] entry, [1] set-up done, [2] last TMA issued, [3] last MMA committed,
-// [4] last epilogue tile stored, [5] tensor memory returned, [6] owner rows reduced and pushed,
+// [4] last epilogue tile stored, [5] tensor memory returned, [6] all deliveries seen,
 // [7] exit.  A debugging and tuning aid; costs a handful of timer reads by single threads.
 constexpr size_t kGemmTraceOff = 1024;
 __device__ __forceinline__ void gemm_trace(const RankView& me, const HeapLayout& lay, int slot) {
@@ -166,9 +190,16 @@ __device__ __forceinline__ void gemm_trace(const RankView& me, const HeapLayout&
     reinterpret_cast<unsigned long long*>(me.heap + lay.ctrl_off + kGemmTraceOff)[slot] = globaltimer_ns();
 }
 
-template <int BN, int STAGES>
+// Offsets (uint32 slots) next to the device-side sequence words in the control region.
+constexpr int kGemmDoneTotalSlot = 3;   // device-side running total of expected deliveries (graph-captured launches)
+constexpr int kGemmDoneSlot = 4;        // the delivery counter the owners' CTAs add to
+constexpr int kGemmEpochSlot = 6;       // device-side running launch number (graph-captured launches)
+
+template <int BN, int STAGES, int A_ROWS>
 struct GemmSmem {
-  alignas(1024) unsigned char a[STAGES][kGemmBM * kGemmBK * 2];
+  // The X stages come first: with A_ROWS < 128 the tensor core reads past a stage's rows into the
+  // next stages (and, for the last one, into the W stages), never outside this structure.
+  alignas(1024) unsigned char a[STAGES][A_ROWS * kGemmBK * 2];
   alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -177,85 +208,112 @@ struct GemmSmem {
   alignas(16) unsigned char epi[4][32 * 128];  // transpose patch of each epilogue warp
   uint32_t tmem_base;
   int abort_flag;
+  int owner_fail;
   float red[kGemmThreads / 32];
 };
+static_assert(kGemmBM * kGemmBK * 2 <= 4 * 64 * kGemmBK * 2, "the W stages must cover what a short X stage leaves to read");
 
-// The owner's work on one of its rows, shared by the warp-per-row and CTA-per-row forms.  `tid` /
-// `nthr` describe the group of threads that shares the row; a thread touches the same vectors in
-// both passes, so no barrier is needed between them.
+// Barrier among the owner warps only (warps 6..11); the GEMM warps never join it.
+__device__ __forceinline__ void owner_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kGemmOwnerThreads) : "memory"); }
+
+// m-tile visited at position j of the tile order.  When the m-tiles divide evenly over the ranks the
+// order interleaves the owners (first tile of every owner, then the second, ...), so that every
+// owner's rows complete at an even pace while the GEMM runs; otherwise it is the identity.
+__device__ __forceinline__ int gemm_mtile_at(int j, int m_tiles, int world, int rows_per_rank) {
+  if (world <= 1 || m_tiles % world != 0 || rows_per_rank % kGemmBM != 0) return j;
+  const int per = m_tiles / world;
+  return (j % world) * per + j / world;
+}
+
+// What a group of threads (`tid` of `nthr`) does for one row: the reduce-scatter owner's side
+// (sum of the world landed copies) and the one-shot receiver's side (the same sum, from the
+// one-shot landing zone).  A thread touches the same vectors in every pass, so no barrier is
+// needed between the passes.
 template <typename T>
 struct RowCtx {
   const RankView* me;
   const HeapLayout* lay;
   const GemmArArgs* args;
   int slot;  // which of the launch's ranks this block row is
-  uint32_t seq;
+  uint32_t epoch;
   int m_tiles, n_tiles;
-  int* fail;  // shared-memory flag of the CTA
+  int* fail;  // shared-memory flag of the thread group
 
-  // Bounded wait until every source rank has delivered every column tile of this row's 32-row group.
+  __device__ bool poll_flag(const uint32_t* fp, int src, int nt, int site) const {
+    uint32_t* abort_word = reinterpret_cast<uint32_t*>(me->heap + lay->ctrl_off + kCtrlAbortOff);
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+      const uint32_t seen = ld_acquire_sys_u32(fp);
+      if (seen == epoch) return true;
+      if ((++spins & 0x3fu) == 0) {
+        if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
+          if (ld_volatile_u32(abort_word) != 0) note_aborted_by_peer(abort_word, me->status, me->rank, site);
+          *fail = 1;
+          return false;
+        }
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > me->timeout_ns) {
+          if (claim_status(abort_word, kTimeout)) {
+            StatusBlock* sb = me->status;
+            sb->rank = uint32_t(me->rank);
+            sb->peer = uint32_t(src);
+            sb->wire = blockIdx.x;
+            sb->step = uint32_t(nt);
+            sb->expected = epoch;
+            sb->seen = seen;
+            sb->where = uint32_t(site);
+            __threadfence_system();
+            sb->code = kTimeout;
+            __threadfence_system();
+          }
+          for (int q = 0; q < me->world; ++q)  // own abort word included
+            st_volatile_u32(reinterpret_cast<uint32_t*>(me->peer[q] + lay->ctrl_off + kCtrlAbortOff), 1u);
+          *fail = 1;
+          return false;
+        }
+      }
+    }
+  }
+
+  // Reduce-scatter: bounded wait until every source rank has delivered every column tile of this
+  // row's 32-row group.
   __device__ bool wait_row_flags(int row, int tid, int nthr) const {
     const int W = me->world;
     const int mt = row / kGemmBM;
     const int grp = (row % kGemmBM) / 32;
-    uint32_t* abort_word = reinterpret_cast<uint32_t*>(me->heap + lay->ctrl_off + kCtrlAbortOff);
     bool ok = true;
     for (int f = tid; f < W * n_tiles && ok; f += nthr) {
       const int src = f / n_tiles, nt = f % n_tiles;
       const uint32_t* fp = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off) +
                            ((size_t(src) * m_tiles + mt) * n_tiles + nt) * 4 + grp;
-      uint32_t spins = 0;
-      uint64_t t0 = 0;
-      for (;;) {
-        const uint32_t seen = ld_acquire_sys_u32(fp);
-        if (seen == seq) break;
-        if ((++spins & 0x3fu) == 0) {
-          if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
-            if (ld_volatile_u32(abort_word) != 0) note_aborted_by_peer(abort_word, me->status, me->rank, 21);
-            *fail = 1;
-            ok = false;
-            break;
-          }
-          const uint64_t now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > me->timeout_ns) {
-            if (claim_status(abort_word, kTimeout)) {
-              StatusBlock* sb = me->status;
-              sb->rank = uint32_t(me->rank);
-              sb->peer = uint32_t(src);
-              sb->wire = blockIdx.x;
-              sb->step = uint32_t(nt);
-              sb->expected = seq;
-              sb->seen = seen;
-              sb->where = 21;
-              __threadfence_system();
-              sb->code = kTimeout;
-              __threadfence_system();
-            }
-            for (int q = 0; q < W; ++q)  // own abort word included
-              st_volatile_u32(reinterpret_cast<uint32_t*>(me->peer[q] + lay->ctrl_off + kCtrlAbortOff), 1u);
-            *fail = 1;
-            ok = false;
-            break;
-          }
-        }
-      }
+      ok = poll_flag(fp, src, nt, 21);
     }
     return ok;
   }
-
-  __device__ uint16_t* my_res_row(int row) const {
-    return reinterpret_cast<uint16_t*>(me->heap + (args->res_out_off ? args->res_out_off : args->out_off)) + size_t(row) * args->N;
+  // One-shot: bounded wait until every source rank has delivered every column tile (of all rows).
+  __device__ bool wait_oneshot_flags(int tid, int nthr) const {
+    const int W = me->world;
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off) + size_t(epoch & 1u) * W * n_tiles;
+    bool ok = true;
+    for (int f = tid; f < W * n_tiles && ok; f += nthr) ok = poll_flag(base + f, f / n_tiles, f % n_tiles, 23);
+    return ok;
   }
 
-  // Sum of the world partial copies in rank order (+ residual), rounded and kept locally; returns
-  // this thread's share of the sum of squares.
-  __device__ float pass1(int i, int row, int tid, int nthr) const {
+  // Where the summed row lives on every rank: res_out if the caller wants it, else out.
+  __device__ size_t sum_off() const { return args->res_out_off ? args->res_out_off : args->out_off; }
+
+  // Sum of the world partial copies of one row in rank order (+ residual), rounded; `copy0` is the
+  // row's copy from source rank 0, the other sources are `src_stride` bytes apart.  The rounded row
+  // goes to the summed-row buffer of every rank in `dest_mask` (bit q = rank q).  Returns this
+  // thread's share of the sum of squares of the rounded values.
+  __device__ float sum_row(const char* copy0, size_t src_stride, int row, int tid, int nthr, uint32_t dest_mask) const {
     constexpr int U = 4;
-    const int W = me->world, N = args->N, rpr = args->rows_per_rank;
+    const int W = me->world, N = args->N;
     const int nvec = N / 8;
     const uint16_t* residual = static_cast<const uint16_t*>(args->residual[slot]);
-    uint16_t* my_res = my_res_row(row);
+    const size_t row_off = sum_off() + size_t(row) * N * 2;
     float ss = 0.f;
     for (int v0 = tid; v0 < nvec; v0 += U * nthr) {
       float a[U][8];
@@ -264,12 +322,12 @@ struct RowCtx {
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[u][e] = 0.f;
       for (int src = 0; src < W; ++src) {
-        const char* base = me->heap + args->landing_off + ((size_t(src) * rpr + i) * size_t(N)) * 2;
+        const char* base = copy0 + size_t(src) * src_stride;
         uint4 x[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int v = v0 + u * nthr;
-          x[u] = v < nvec ? *reinterpret_cast<const uint4*>(base + size_t(v) * 16) : make_uint4(0, 0, 0, 0);
+          x[u] = v < nvec ? ld_volatile_u4(base + size_t(v) * 16) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) acc8_add<T>(a[u], x[u]);
@@ -289,7 +347,10 @@ struct RowCtx {
         const int v = v0 + u * nthr;
         if (v >= nvec) continue;
         const uint4 o = acc8_pack<T>(a[u]);
-        *reinterpret_cast<uint4*>(my_res + size_t(v) * 8) = o;
+        for (int k = 0; k < W; ++k) {
+          const int q = (me->rank + k) % W;
+          if (dest_mask & (1u << q)) *reinterpret_cast<uint4*>(me->peer[q] + row_off + size_t(v) * 16) = o;
+        }
         float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         acc8_add<T>(b, o);
 #pragma unroll
@@ -299,27 +360,27 @@ struct RowCtx {
     return ss;
   }
 
-  // Normalise (if asked) and push the row to every rank.
-  __device__ void pass2(int row, int tid, int nthr, float inv) const {
+  // out[row] = summed row * inv * gamma (or a plain copy without the norm); everything is local.
+  __device__ void finish_row(int row, int tid, int nthr, float inv) const {
     constexpr int U = 4;
-    const int W = me->world, N = args->N;
+    const int N = args->N;
     const int nvec = N / 8;
-    const int rank = me->rank;
-    const uint16_t* my_res = my_res_row(row);
+    const char* src = me->heap + sum_off() + size_t(row) * N * 2;
+    char* dst = me->heap + args->out_off + size_t(row) * N * 2;
+    if (!args->with_norm && src == dst) return;
     const uint4* gamma = static_cast<const uint4*>(args->gamma[slot]);
-    const bool mute = (me->flags & kMuteSends) != 0;
     for (int v0 = tid; v0 < nvec; v0 += U * nthr) {
       uint4 x[U], g[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int v = v0 + u * nthr;
-        x[u] = v < nvec ? *reinterpret_cast<const uint4*>(my_res + size_t(v) * 8) : make_uint4(0, 0, 0, 0);
+        x[u] = v < nvec ? ld_volatile_u4(src + size_t(v) * 16) : make_uint4(0, 0, 0, 0);
         g[u] = (args->with_norm && v < nvec) ? gamma[v] : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int v = v0 + u * nthr;
-        if (v >= nvec || mute) continue;
+        if (v >= nvec) continue;
         uint4 y = x[u];
         if (args->with_norm) {
           const uint32_t xs[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
@@ -333,21 +394,16 @@ struct RowCtx {
           }
           y = make_uint4(ys[0], ys[1], ys[2], ys[3]);
         }
-        for (int k = 0; k < W; ++k) {
-          const int q = (rank + k) % W;
-          *reinterpret_cast<uint4*>(me->peer[q] + args->out_off + (size_t(row) * N + size_t(v) * 8) * 2) = y;
-          if (args->res_out_off && q != rank)
-            *reinterpret_cast<uint4*>(me->peer[q] + args->res_out_off + (size_t(row) * N + size_t(v) * 8) * 2) = x[u];
-        }
+        *reinterpret_cast<uint4*>(dst + size_t(v) * 16) = y;
       }
     }
   }
 };
 
-template <typename T, int BN, int STAGES>
+template <typename T, int BN, int STAGES, int A_ROWS>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_constant__ GemmArArgs args) {
   extern __shared__ unsigned char smem_raw[];
-  using Smem = GemmSmem<BN, STAGES>;
+  using Smem = GemmSmem<BN, STAGES, A_ROWS>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const RankView& me = args.k.v[blockIdx.y];
@@ -363,16 +419,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   const int k_iters = (K + kGemmBK - 1) / kGemmBK;
   const int total_tiles = m_tiles * n_tiles;
   const int rpr = args.rows_per_rank;
-  // Graph-captured launches: the running flag value and delivery total live on the device and
+  const bool oneshot = args.mode == kGemmModeOneShot;
+  const uint64_t timeout_ns = me.timeout_ns;
+  // Graph-captured launches: launch number and delivery total live on the device and
   // args.done_target then holds this launch's increment instead of an absolute value.
-  uint32_t seq = me.seq;
+  uint32_t epoch = args.epoch;
   uint32_t done_target = args.done_target;
   if (me.seq_dev) {
-    seq += ld_volatile_u32(me.seq_dev);
-    done_target += ld_volatile_u32(me.seq_dev + 3);
+    epoch += ld_volatile_u32(me.seq_dev + kGemmEpochSlot);
+    done_target += ld_volatile_u32(me.seq_dev + kGemmDoneTotalSlot);
   }
   constexpr uint32_t kTmemCols = 2 * BN;
   const uint32_t stage_bytes = uint32_t(args.a_box_rows + BN) * kGemmBK * 2;
+  const bool mute = (me.flags & kMuteSends) != 0;
 
   // ---- set-up ---------------------------------------------------------------------------
   if (threadIdx.x == 0) gemm_trace(me, lay, 0);
@@ -386,6 +445,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       mbar_init(&s.acc_empty[i], 4);  // one arrival per epilogue warp
     }
     s.abort_flag = 0;
+    s.owner_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -399,18 +459,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   volatile int* abort_flag = &s.abort_flag;
   if (threadIdx.x == 0) gemm_trace(me, lay, 1);
 
-  // ---- phase 1: GEMM + reduce-scatter epilogue ---------------------------------------------
+  RowCtx<T> rc;
+  rc.me = &me;
+  rc.lay = &lay;
+  rc.args = &args;
+  rc.slot = int(blockIdx.y);
+  rc.epoch = epoch;
+  rc.m_tiles = m_tiles;
+  rc.n_tiles = n_tiles;
+  rc.fail = &s.owner_fail;
+
+  // ---- GEMM + exchange: four roles run side by side ---------------------------------------------
   if (warp == 0) {
     if (lane == 0) {
       const CUtensorMap* ta = &args.tma_a[blockIdx.y];
       const CUtensorMap* tb = &args.tma_b[blockIdx.y];
       uint32_t it = 0;
       for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G) {
-        const int mt = t / n_tiles, nt = t % n_tiles;
+        const int mt = gemm_mtile_at(t / n_tiles, m_tiles, W, rpr), nt = t % n_tiles;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int st = int(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag)) break;
+          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, timeout_ns)) break;
           mbar_expect_tx(&s.full[st], stage_bytes);
           tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
           tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
@@ -420,7 +490,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       // copies in flight land in this CTA's shared memory: wait for the ones still pending
       for (uint32_t back = 0; back < uint32_t(STAGES) && back < it; ++back) {
         const uint32_t j = it - 1 - back;
-        mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1u, abort_flag);
+        mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1u, abort_flag, timeout_ns);
       }
     }
   } else if (warp == 1) {
@@ -430,14 +500,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
         const uint32_t buf = tile_i & 1u;
         const uint32_t use = tile_i >> 1;  // how often this accumulator buffer has been used before
-        if (!mbar_wait(&s.acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) break;
+        if (!mbar_wait(&s.acc_empty[buf], (use & 1u) ^ 1u, abort_flag, timeout_ns)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         bool ok = true;
         for (int kb = 0; kb < k_iters; ++kb, ++it) {
           const int st = int(it % STAGES);
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&s.full[st], ph, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&s.full[st], ph, abort_flag, timeout_ns)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st]));
           const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st]));
@@ -457,84 +527,139 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int lane_group = warp & 3;
     uint32_t tile_i = 0;
+    const size_t os_landing = args.landing_off + size_t(epoch & 1u) * args.oneshot_half_bytes;
     for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
-      const int mt = t / n_tiles, nt = t % n_tiles;
+      const int mt = gemm_mtile_at(t / n_tiles, m_tiles, W, rpr), nt = t % n_tiles;
       const uint32_t buf = tile_i & 1u;
       const uint32_t use = tile_i >> 1;
-      if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag)) break;
+      if (!mbar_wait(&s.acc_full[buf], use & 1u, abort_flag, timeout_ns)) break;
       tc_fence_after_sync();
-      // The accumulator comes out of tensor memory one row per lane.  Written like that, a warp
-      // store would be 32 pieces of 16 bytes 2 N bytes apart - poison for NVLink.  So each 64-column
-      // chunk is rounded, transposed through a swizzled 4 KiB shared-memory patch and stored with
-      // eight lanes per row: every store instruction writes four full 128-byte lines.
-      unsigned char* patch = s.epi[lane_group];
-      const bool mute = (me.flags & kMuteSends) != 0;
+      const int first_row = mt * kGemmBM + lane_group * 32;
+      if (first_row < M) {
+        // The accumulator comes out of tensor memory one row per lane.  Written like that, a warp
+        // store would be 32 pieces of 16 bytes 2 N bytes apart - poison for NVLink.  So each 64-column
+        // chunk is rounded, transposed through a swizzled 4 KiB shared-memory patch and stored with
+        // eight lanes per row: every store instruction writes four full 128-byte lines.
+        unsigned char* patch = s.epi[lane_group];
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
-        uint32_t acc[32];
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t acc[32];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          tmem_ld_32cols(tmem_base + (uint32_t(lane_group * 32) << 16) + buf * BN + uint32_t(c + 32 * h), acc);
-          tmem_ld_wait();
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld_32cols(tmem_base + (uint32_t(lane_group * 32) << 16) + buf * BN + uint32_t(c + 32 * h), acc);
+            tmem_ld_wait();
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = Cvt<T>::down(__uint_as_float(acc[8 * v + 0]), __uint_as_float(acc[8 * v + 1]));
-            o.y = Cvt<T>::down(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
-            o.z = Cvt<T>::down(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
-            o.w = Cvt<T>::down(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
-            const int chunk = 4 * h + v;  // 16-byte chunk of this lane's 128-byte row
-            *reinterpret_cast<uint4*>(patch + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = o;
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = Cvt<T>::down(__uint_as_float(acc[8 * v + 0]), __uint_as_float(acc[8 * v + 1]));
+              o.y = Cvt<T>::down(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
+              o.z = Cvt<T>::down(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
+              o.w = Cvt<T>::down(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
+              const int chunk = 4 * h + v;  // 16-byte chunk of this lane's 128-byte row
+              *reinterpret_cast<uint4*>(patch + lane * 128 + ((chunk ^ (lane & 7)) * 16)) = o;
+            }
           }
-        }
-        __syncwarp();
+          __syncwarp();
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int pr = it * 4 + (lane >> 3);  // row of the patch this lane stores
-          const int chunk = lane & 7;
-          const uint4 o = *reinterpret_cast<const uint4*>(patch + pr * 128 + ((chunk ^ (pr & 7)) * 16));
-          const int row = mt * kGemmBM + lane_group * 32 + pr;
-          if (row < M && !mute) {
-            const int owner = row / rpr;
-            char* dst = me.peer[owner] + args.landing_off +
-                        ((size_t(rank) * rpr + size_t(row - owner * rpr)) * size_t(N) + size_t(nt) * BN + size_t(c) + size_t(chunk) * 8) * 2;
-            *reinterpret_cast<uint4*>(dst) = o;
+          for (int it = 0; it < 8; ++it) {
+            const int pr = it * 4 + (lane >> 3);  // row of the patch this lane stores
+            const int chunk = lane & 7;
+            const uint4 o = *reinterpret_cast<const uint4*>(patch + pr * 128 + ((chunk ^ (pr & 7)) * 16));
+            const int row = first_row + pr;
+            if (row < M && !mute) {
+              const size_t col = size_t(nt) * BN + size_t(c) + size_t(chunk) * 8;
+              if (oneshot) {
+                // every rank gets this rank's copy: [source][row][N]
+                const size_t off = os_landing + ((size_t(rank) * M + size_t(row)) * size_t(N) + col) * 2;
+                for (int k = 0; k < W; ++k) *reinterpret_cast<uint4*>(me.peer[(rank + k) % W] + off) = o;
+              } else {
+                const int owner = row / rpr;
+                char* dst = me.peer[owner] + args.landing_off +
+                            ((size_t(rank) * rpr + size_t(row - owner * rpr)) * size_t(N) + col) * 2;
+                *reinterpret_cast<uint4*>(dst) = o;
+              }
+            }
           }
+          __syncwarp();  // the patch is rewritten by the next chunk
         }
-        __syncwarp();  // the patch is rewritten by the next chunk
       }
       // accumulator buffer free again
       tc_fence_before_sync();
-      __syncwarp();  // also orders this warp's 32 row stores before the flag stores below
+      __syncwarp();  // also orders this warp's row stores before the flag stores below
       if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
-      // One flag per (source, tile, 32-row group) on every owner that got rows from this warp:
-      // no barrier between the epilogue warps is needed, each warp answers for its own rows.
-      const int first_row = mt * kGemmBM + lane_group * 32;
-      if (first_row < M && !(me.flags & kMuteSends)) {
-        int last_row = first_row + 31;
-        if (last_row > M - 1) last_row = M - 1;
-        const int q = first_row / rpr + lane;
-        if (q <= last_row / rpr) {
-          // st.release.sys orders this warp's row stores (made visible to this lane by the
-          // __syncwarp above) before the flag; no separate fence
-          uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[q] + args.flags_off) +
-                        ((size_t(rank) * m_tiles + mt) * n_tiles + nt) * 4 + lane_group;
-          st_release_sys_u32(f, seq);
+      if (first_row < M && !mute) {
+        // st.release.sys orders this warp's row stores (made visible to the storing lane by the
+        // __syncwarp above) before the flag; no separate fence
+        if (oneshot) {
+          // one flag per (source, column tile) on every rank; rows 0..31 are all there is
+          if (lane < W) {
+            uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[lane] + args.flags_off) +
+                          (size_t(epoch & 1u) * W + size_t(rank)) * n_tiles + nt;
+            st_release_sys_u32(f, epoch);
+          }
+        } else {
+          // one flag per (source, tile, 32-row group) on every owner that got rows from this warp:
+          // no barrier between the epilogue warps is needed, each warp answers for its own rows
+          int last_row = first_row + 31;
+          if (last_row > M - 1) last_row = M - 1;
+          const int q = first_row / rpr + lane;
+          if (q <= last_row / rpr) {
+            uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[q] + args.flags_off) +
+                          ((size_t(rank) * m_tiles + mt) * n_tiles + nt) * 4 + lane_group;
+            st_release_sys_u32(f, epoch);
+          }
         }
       }
     }
+    if (threadIdx.x == 64) gemm_trace(me, lay, 4);
+  } else if (!oneshot) {
+    // ---- owner side (warps 6..11), concurrent with the GEMM: one row at a time per CTA, in the order
+    // in which the rows complete ----------------------------------------------------------------------
+    const int otid = int(threadIdx.x) - (kGemmThreads - kGemmOwnerThreads);
+    const int owarp = otid >> 5;
+    const int row0 = rank * rpr;
+    int nrows = M - row0;
+    if (nrows > rpr) nrows = rpr;
+    if (nrows < 0) nrows = 0;
+    // owned rows in completion order: the m-tiles of this rank as the tile order visits them
+    const int own_tiles = (nrows + kGemmBM - 1) / kGemmBM;
+    const bool interleaved = gemm_mtile_at(1, m_tiles, W, rpr) != 1 || m_tiles <= 1;
+    (void)interleaved;
+    float* inv_all = nullptr;
+    for (int i = int(blockIdx.x); i < nrows; i += G) {
+      // position i of the owned rows -> row: rows are spread so that consecutive CTAs take rows of the
+      // same 32-row group (their flags arrive together)
+      const int row = row0 + i;
+      (void)own_tiles;
+      rc.wait_row_flags(row, otid, kGemmOwnerThreads);
+      owner_bar_sync();
+      if (s.owner_fail) break;
+      const char* copy0 = me.heap + args.landing_off + size_t(i) * size_t(N) * 2;
+      float ss = rc.sum_row(copy0, size_t(rpr) * size_t(N) * 2, row, otid, kGemmOwnerThreads, mute ? 0u : ((1u << W) - 1u));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s.red[owarp] = ss;
+      owner_bar_sync();
+      if (otid < W && !mute) {
+        float tot = 0.f;
+        for (int w = 0; w < kGemmOwnerWarps; ++w) tot += s.red[w];
+        const float inv = rsqrtf(tot / float(N) + args.eps);
+        inv_all = reinterpret_cast<float*>(me.peer[otid] + args.inv_off);
+        inv_all[row] = inv;
+      }
+      owner_bar_sync();  // s.red is reused by the next row
+    }
   }
 
-  if (threadIdx.x == 64) gemm_trace(me, lay, 4);
-  // ---- tensor memory goes back before anything waits on a peer ---------------------------------
+  // ---- everybody meets; tensor memory goes back --------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0) gemm_trace(me, lay, 5);
+  uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
   if (*abort_flag) {
     if (threadIdx.x == 0) {
-      uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
       st_volatile_u32(abort_word, 1u);
       if (claim_status(abort_word, kTimeout)) {
         StatusBlock* sb = me.status;
@@ -549,106 +674,95 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     }
     return;
   }
-
-  // ---- phase 2/3: owner reduce (+ residual, RMSNorm) and all-gather push ------------------------
-  // Many owned rows: one row per warp (six rows in flight per CTA, no block barrier).  Few rows
-  // (decode): one row per CTA so that all threads share the row.
-  const int row0 = rank * rpr;
-  int nrows = M - row0;
-  if (nrows > rpr) nrows = rpr;
-  if (nrows < 0) nrows = 0;
   const int nthreads = int(blockDim.x);
   const int nwarps = nthreads >> 5;
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __syncthreads();
-  RowCtx<T> rc;
-  rc.me = &me;
-  rc.lay = &lay;
-  rc.args = &args;
-  rc.slot = int(blockIdx.y);
-  rc.seq = seq;
-  rc.m_tiles = m_tiles;
-  rc.n_tiles = n_tiles;
-  rc.fail = &s_fail;
-  if (nrows >= 2 * G * nwarps) {
-    for (int i = int(blockIdx.x) * nwarps + warp; i < nrows; i += G * nwarps) {
-      // the verdict must be the same for the whole warp: the shuffles below need every lane
-      if (!__all_sync(0xffffffffu, rc.wait_row_flags(row0 + i, lane, 32))) break;
-      float ss = rc.pass1(i, row0 + i, lane, 32);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      rc.pass2(row0 + i, lane, 32, rsqrtf(ss / float(N) + args.eps));
-    }
-  } else {
-    for (int i = int(blockIdx.x); i < nrows; i += G) {
-      const bool ok = rc.wait_row_flags(row0 + i, int(threadIdx.x), nthreads);
-      (void)ok;
-      __syncthreads();
-      if (s_fail) break;
-      float ss = rc.pass1(i, row0 + i, int(threadIdx.x), nthreads);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s.red[warp] = ss;
-      __syncthreads();
-      float tot = 0.f;
-      for (int w = 0; w < nwarps; ++w) tot += s.red[w];
-      rc.pass2(row0 + i, int(threadIdx.x), nthreads, rsqrtf(tot / float(N) + args.eps));
-      __syncthreads();  // s.red is reused by the next row
-    }
-  }
+  bool failed = s.owner_fail != 0;
 
-  // ---- phase 4: tell everyone this CTA has delivered; CTA 0 waits for all deliveries ---------------
-  __syncthreads();
-  if (threadIdx.x == 0) gemm_trace(me, lay, 6);
-  uint32_t* abort_word = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlAbortOff);
-  uint32_t* done = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlSeqOff) + 4;
-  if (threadIdx.x < uint32_t(W) && !(me.flags & kMuteSends) && !s_fail) {
-    // release semantics of the reduction order the CTA's pushes (synchronised by the barrier above) before it
-    red_release_sys_add(reinterpret_cast<uint32_t*>(me.peer[threadIdx.x] + lay.ctrl_off + kCtrlSeqOff) + 4, 1u);
-  }
-  if (blockIdx.x == 0 && threadIdx.x == 0 && !s_fail) {
-    uint32_t spins = 0;
-    uint64_t t0 = 0;
-    for (;;) {
-      const uint32_t seen = ld_acquire_sys_u32(done);
-      if (int32_t(seen - done_target) >= 0) break;
-      if ((++spins & 0x3fu) == 0) {
-        if (ld_volatile_u32(abort_word) != 0) {
-          note_aborted_by_peer(abort_word, me.status, rank, 22);
-          break;
-        }
-        const uint64_t now = globaltimer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > me.timeout_ns) {
-          st_volatile_u32(abort_word, 1u);
-          if (claim_status(abort_word, kTimeout)) {
-            StatusBlock* sb = me.status;
-            sb->rank = uint32_t(rank);
-            sb->peer = 0;
-            sb->wire = 0;
-            sb->expected = done_target;
-            sb->seen = seen;
-            sb->where = 22;
-            __threadfence_system();
-            sb->code = kTimeout;
-            __threadfence_system();
+  if (oneshot) {
+    // ---- one-shot: every rank adds the world copies of each row, the residual, and normalises -----
+    const size_t os_landing = args.landing_off + size_t(epoch & 1u) * args.oneshot_half_bytes;
+    if (int(blockIdx.x) < M) {
+      rc.wait_oneshot_flags(int(threadIdx.x), nthreads);
+      __syncthreads();
+      failed = s.owner_fail != 0;
+      for (int row = int(blockIdx.x); row < M && !failed; row += G) {
+        const char* copy0 = me.heap + os_landing + size_t(row) * size_t(N) * 2;
+        float ss = rc.sum_row(copy0, size_t(M) * size_t(N) * 2, row, int(threadIdx.x), nthreads, 1u << rank);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) s.red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < nwarps; ++w) tot += s.red[w];
+        rc.finish_row(row, int(threadIdx.x), nthreads, rsqrtf(tot / float(N) + args.eps));
+        __syncthreads();  // s.red is reused by the next row
+      }
+    }
+    if (threadIdx.x == 0) gemm_trace(me, lay, 6);
+  } else {
+    // ---- reduce-scatter: tell everyone this CTA has delivered, wait for all deliveries, then
+    // normalise a share of the rows locally ------------------------------------------------------------
+    uint32_t* done = reinterpret_cast<uint32_t*>(me.heap + lay.ctrl_off + kCtrlSeqOff) + kGemmDoneSlot;
+    if (threadIdx.x < uint32_t(W) && !mute && !failed) {
+      // release semantics of the reduction order the CTA's pushes (synchronised by the barrier above) before it
+      red_release_sys_add(reinterpret_cast<uint32_t*>(me.peer[threadIdx.x] + lay.ctrl_off + kCtrlSeqOff) + kGemmDoneSlot, 1u);
+    }
+    if (threadIdx.x == 0 && !failed) {
+      uint32_t spins = 0;
+      uint64_t t0 = 0;
+      for (;;) {
+        const uint32_t seen = ld_acquire_sys_u32(done);
+        if (int32_t(seen - done_target) >= 0) break;
+        if ((++spins & 0x3fu) == 0) {
+          if (ld_volatile_u32(abort_word) != 0) {
+            note_aborted_by_peer(abort_word, me.status, rank, 22);
+            s.owner_fail = 1;
+            break;
           }
-          break;
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > timeout_ns) {
+            st_volatile_u32(abort_word, 1u);
+            if (claim_status(abort_word, kTimeout)) {
+              StatusBlock* sb = me.status;
+              sb->rank = uint32_t(rank);
+              sb->peer = 0;
+              sb->wire = blockIdx.x;
+              sb->expected = done_target;
+              sb->seen = seen;
+              sb->where = 22;
+              __threadfence_system();
+              sb->code = kTimeout;
+              __threadfence_system();
+            }
+            s.owner_fail = 1;
+            break;
+          }
         }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) gemm_trace(me, lay, 6);
+    failed = s.owner_fail != 0;
+    if (!failed && (args.with_norm || args.res_out_off != 0)) {
+      const float* inv = reinterpret_cast<const float*>(me.heap + args.inv_off);
+      for (int row = int(blockIdx.x); row < M; row += G) {
+        float iv = 1.f;
+        if (args.with_norm) iv = __uint_as_float(ld_volatile_u32(inv + row));
+        rc.finish_row(row, int(threadIdx.x), nthreads, iv);
       }
     }
   }
   if (threadIdx.x == 0) gemm_trace(me, lay, 7);
   if (me.seq_dev) {
-    // the last CTA to leave advances the device-side flag value and delivery total
+    // the last CTA to leave advances the device-side launch number and delivery total
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
       if (atomicAdd(me.seq_dev + 1, 1u) == gridDim.x - 1) {
         me.seq_dev[1] = 0;
-        me.seq_dev[0] += me.seq_step;
-        me.seq_dev[3] += args.done_target;
+        me.seq_dev[kGemmEpochSlot] += 1;
+        me.seq_dev[kGemmDoneTotalSlot] += args.done_target;
         __threadfence();
       }
     }

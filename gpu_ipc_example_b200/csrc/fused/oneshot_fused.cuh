@@ -69,9 +69,8 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
   }
   const int64_t ntx = ceil_div64(d1 - d0, B::kPayloadDw);
 
-  __shared__ float s_sumsq[kFusedMaxRowsPerCta];
+  __shared__ float s_part[32];
   __shared__ int s_abort;
-  if (threadIdx.x < kFusedMaxRowsPerCta) s_sumsq[threadIdx.x] = 0.f;
   if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
 
@@ -128,28 +127,6 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
       B::acc_to_msg(v, a);
       B::restore(v);
       B::store(res_out, dw, d1, -1, v);
-      // sum of squares of the rounded values, per row
-      float ss = 0.f;
-      const int64_t first_row = dw / row_dw;
-      const int64_t last_dw = min64(dw + B::kPayloadDw, d1) - 1;
-      const bool one_row = (last_dw / row_dw) == first_row;
-      if (lane < 30) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int64_t idx = dw + 4 * lane + e;
-          if (idx < d1) {
-            float2 x = Cvt<T>::up(v.d[e]);
-            const float s = x.x * x.x + x.y * x.y;
-            if (one_row) ss += s;
-            else atomicAdd(&s_sumsq[int(idx / row_dw) - row0], s);
-          }
-        }
-      }
-      if (one_row) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) atomicAdd(&s_sumsq[int(first_row) - row0], ss);
-      }
     } else {
       // scale and cast; lanes 30/31 carry displaced dwords, so restore first
 #pragma unroll
@@ -169,10 +146,29 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
     const float eps = scale;
     const uint4* gamma = reinterpret_cast<const uint4*>(me.aux[1]);
     const int row_vec = hidden / 8;
+    // The row statistic is taken from the rounded sums this CTA has just written, by a reduction whose
+    // order depends on nothing but the thread index: every rank computes the same bits (a floating-point
+    // atomic would add the warps' shares in the order they happen to arrive).
     for (int rr = 0; rr < nrows; ++rr) {
-      const float inv = rsqrtf(s_sumsq[rr] / float(hidden) + eps);
       const uint4* src = reinterpret_cast<const uint4*>(res_out + (int64_t(row0 + rr)) * row_dw);
       uint4* dst = reinterpret_cast<uint4*>(out + (int64_t(row0 + rr)) * row_dw);
+      float ss = 0.f;
+      for (int i = int(threadIdx.x); i < row_vec; i += int(blockDim.x)) {
+        const uint4 x = src[i];
+        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = Cvt<T>::up(xs[e]);
+          ss += xf.x * xf.x + xf.y * xf.y;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_part[warp] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < warps; ++w) tot += s_part[w];
+      const float inv = rsqrtf(tot / float(hidden) + eps);
       for (int i = int(threadIdx.x); i < row_vec; i += int(blockDim.x)) {
         const uint4 x = src[i];
         const uint4 g = gamma[i];
@@ -187,6 +183,7 @@ __global__ void __launch_bounds__(1024) oneshot_fused_kernel(const __grid_consta
         }
         dst[i] = make_uint4(ys[0], ys[1], ys[2], ys[3]);
       }
+      __syncthreads();  // s_part is reused by the next row
     }
   }
 

@@ -311,7 +311,15 @@ class Communicator:
             raise CollectiveError(str(e)) from None
 
     def reset(self):
+        """After a failed collective: waits for the device, clears rings, flags and the status (collective
+        in a multi-process world).  The cached workspaces of the fused GEMM kernels are cleared too, so that
+        no flag left by an interrupted launch can be taken for a later one."""
         self._C.reset(self._h)
+        for wsp, _, _ in self.__dict__.get("_gemm_buffers", {}).values():
+            for t in (wsp if self._virtual else [wsp]):
+                t.zero_()
+        torch.cuda.synchronize()
+        self.barrier()
 
     def barrier(self):
         self._C.host_barrier(self._h)

@@ -57,6 +57,8 @@ def parse_json_rows(text: str, world: int, collective: str = "all_reduce", place
         r = json.loads(line)
         if r["world"] != world or r["collective"] != collective or r["placement"] != placement:
             continue
+        if r["algo"] in ("auto", "allgather_auto") or r.get("timing") == "graph_replay":
+            continue
         if symmetric is not None and bool(r.get("symmetric")) != symmetric and r["algo"] in ("bulk", "nvls"):
             continue
         tables.setdefault(r["algo"], {})[int(r["elements"])] = float(r["us_median"])
