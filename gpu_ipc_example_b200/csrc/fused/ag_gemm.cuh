@@ -164,8 +164,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, me.timeout_ns)) break;
           mbar_expect_tx(&s.full[st], kStageBytes);
-          tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
-          tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
+          tma_load_2d(s.a[st][0], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
+          tma_load_2d(s.b[st][0], tb, &s.full[st], kb * kGemmBK, nt * BN);
         }
       }
       for (uint32_t back = 0; back < uint32_t(STAGES) && back < it; ++back) {
@@ -189,8 +189,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&s.full[st], ph, abort_flag, me.timeout_ns)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st]));
-          const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st]));
+          const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st][0]));
+          const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st][0]));
 #pragma unroll
           for (int k = 0; k < kGemmBK / 16; ++k)
             umma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);

@@ -40,8 +40,7 @@ CollInfo fused_allreduce_residual_rmsnorm(Comm& comm, DType t, const FusedNormPt
   // Geometry: a CTA owns whole rows; its warps share the row's transactions.
   const int64_t row_dw = hidden / 2;
   const int64_t row_tx = ceil_div64(row_dw, 120);
-  // few rows: 32 warps per CTA shorten the per-warp chain of steps
-  const int64_t want_warps = rows < 8 ? 32 : 16;
+  const int64_t want_warps = kFusedMaxThreads / 32;
   int warps = int(std::max<int64_t>(4, round_up64(std::min<int64_t>(row_tx, want_warps), 4)));
   int threads = warps * 32;
   int cap = std::min(comm.resident_ctas(fn, threads, 0), kMaxOneShotWires / warps);

@@ -22,9 +22,9 @@ constexpr int kStages64 = 8;    // 8 x (16 KiB +  8 KiB) = 192 KiB
 constexpr int kStagesDecode = 16;  // 16 x (4 KiB + 8 KiB) = 192 KiB: M <= 32, the X stage holds 32 rows
 constexpr int kDecodeRows = 32;
 
-template <typename T, int BN, int STAGES, int A_ROWS>
+template <typename T, int BN, int STAGES, int A_ROWS, int KSUB = 1>
 const void* kernel_ptr() {
-  return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES, A_ROWS>);
+  return reinterpret_cast<const void*>(&gemm_ar_kernel<T, BN, STAGES, A_ROWS, KSUB>);
 }
 
 // Tensor maps depend only on (pointer, extents, box, type): weights and activation buffers are
@@ -72,8 +72,9 @@ size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 // Which exchange a problem uses: one-shot for decode-sized M (every rank gets every partial, one NVLink
 // hop), reduce-scatter + all-gather otherwise.  B200IPC_GEMM_MODE=rs|oneshot overrides (oneshot only
 // where M allows it).
-int gemm_mode_for(int64_t M) {
-  int mode = M <= kGemmOneShotMaxRows ? kGemmModeOneShot : kGemmModeReduceScatter;
+int gemm_mode_for(int64_t M, bool with_norm, bool has_residual) {
+  // the one-shot form computes either the plain sum or sum + residual followed by RMSNorm
+  int mode = (M <= kGemmOneShotMaxRows && with_norm == has_residual) ? kGemmModeOneShot : kGemmModeReduceScatter;
   if (const char* e = std::getenv("B200IPC_GEMM_MODE")) {
     if (std::strcmp(e, "rs") == 0) mode = kGemmModeReduceScatter;
   }
@@ -88,10 +89,10 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
   const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
   // room for either form of the exchange, so that the choice can change between calls
   const size_t rs_landing = size_t(world) * size_t(rpr) * size_t(N) * 2;
-  const size_t os_landing = M <= kGemmOneShotMaxRows ? 2 * up256(size_t(world) * size_t(M) * size_t(N) * 2) : 0;
+  const size_t os_landing = M <= kGemmOneShotMaxRows ? size_t(M) * size_t(N) * 2 : 0;
   w.landing_bytes = up256(std::max(rs_landing, os_landing));
   const size_t rs_flags = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
-  const size_t os_flags = 2 * size_t(world) * size_t(N / 64) * sizeof(uint32_t);
+  const size_t os_flags = size_t(N / 64) * sizeof(uint32_t);
   w.flags_bytes = up256(std::max(rs_flags, os_flags));
   w.inv_bytes = up256(size_t(M) * sizeof(float));
   return w;
@@ -105,7 +106,7 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   B200_REQUIRE(K % 8 == 0, "K must be a multiple of 8");
   B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
-  const int mode = gemm_mode_for(M);
+  const int mode = gemm_mode_for(M, with_norm, ptrs[0].residual != nullptr && ptrs[0].res_out != nullptr);
   // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
   // cut the operand traffic per FLOP for large M.
   const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
@@ -114,8 +115,19 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   size_t smem;
   const bool h = t == DType::F16;
   if (decode) {
-    fn = h ? kernel_ptr<__half, 64, kStagesDecode, kDecodeRows>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode, kDecodeRows>();
-    smem = sizeof(GemmSmem<64, kStagesDecode, kDecodeRows>) + 1024;
+    // sub-tiles per stage (contiguous bytes per weight row and stage = 128 x this); the ring always holds 192 KiB
+    int ksub = 2;
+    if (const char* e = std::getenv("B200IPC_GEMM_KSUB")) ksub = std::atoi(e);
+    if (ksub == 4) {
+      fn = h ? kernel_ptr<__half, 64, kStagesDecode / 4, kDecodeRows, 4>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode / 4, kDecodeRows, 4>();
+      smem = sizeof(GemmSmem<64, kStagesDecode / 4, kDecodeRows, 4>) + 1024;
+    } else if (ksub == 1) {
+      fn = h ? kernel_ptr<__half, 64, kStagesDecode, kDecodeRows, 1>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode, kDecodeRows, 1>();
+      smem = sizeof(GemmSmem<64, kStagesDecode, kDecodeRows, 1>) + 1024;
+    } else {
+      fn = h ? kernel_ptr<__half, 64, kStagesDecode / 2, kDecodeRows, 2>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode / 2, kDecodeRows, 2>();
+      smem = sizeof(GemmSmem<64, kStagesDecode / 2, kDecodeRows, 2>) + 1024;
+    }
   } else if (BN == 64) {
     fn = h ? kernel_ptr<__half, 64, kStages64, kGemmBM>() : kernel_ptr<__nv_bfloat16, 64, kStages64, kGemmBM>();
     smem = sizeof(GemmSmem<64, kStages64, kGemmBM>) + 1024;
@@ -190,11 +202,22 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   args.inv_off = args.flags_off + ws.flags_bytes;
   args.out_off = out_off;
   args.res_out_off = res_off;
-  args.oneshot_half_bytes = up256(size_t(W) * size_t(M) * size_t(N) * 2);
   args.epoch = comm.take_gemm_epoch();
   if (mode == kGemmModeReduceScatter) {
     const uint32_t deliveries = uint32_t(W) * uint32_t(ctas);
     args.done_target = comm.device_seq() ? deliveries : comm.take_done(deliveries);
+  } else {
+    // flag-in-data sequence numbers of the exchange: a CTA's warps share the transactions of its rows
+    B200_REQUIRE(N % 8 == 0 && int64_t(ctas) * (kGemmThreads / 32) <= kMaxOneShotWires, "too many CTAs for the one-shot exchange");
+    const int64_t per = (M + ctas - 1) / ctas;
+    const int64_t steps = ceil_div64(ceil_div64(per * (N / 2), 120), kGemmThreads / 32);
+    const uint32_t adv = uint32_t(steps + 1);
+    const uint32_t first = comm.take_seq(adv);
+    for (int i = 0; i < comm.nlocal(); ++i) {
+      args.k.v[i].seq = first;
+      args.k.v[i].seq_step = adv;
+      B200_REQUIRE(!with_norm || (reinterpret_cast<uintptr_t>(ptrs[i].residual) & 15) == 0, "residual must be 16-byte aligned");
+    }
   }
 
   void* params[] = {&args};

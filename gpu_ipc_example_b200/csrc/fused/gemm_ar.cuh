@@ -19,11 +19,11 @@
 //     even pace.  A delivery counter per rank tells when all owners are done; then every rank
 //     normalises the rows locally (out = sum * 1/rms * gamma), so only ONE tensor crosses the
 //     links in the all-gather.
-//   one-shot (M <= 32, decode):  the epilogue stores each finished tile into EVERY rank (one
-//     NVLink hop, no owner, no all-gather); each rank adds the world copies of a row, the
-//     residual, and normalises.  Landing zone and flags alternate between two halves by launch
-//     parity: a rank can be at most one launch ahead of a peer, so it never overwrites rows a
-//     peer still reads.
+//   one-shot (M <= 32, decode):  the epilogue keeps the rank's partial product in LOCAL memory
+//     (one flag per column tile, device scope); the CTA that holds a row then runs the one-shot
+//     flag-in-data exchange of fused/oneshot_fused.cuh on it without leaving the kernel: LL512
+//     transactions to every peer (no fence, one NVLink hop), the world copies added in rank order,
+//     + residual, RMSNorm.  No owner, no all-gather, no system-scope release on the critical path.
 //
 // Small M is a weight-streaming problem: the X stage of the ring shrinks to the rows that
 // exist, which buys a ring deep enough (16 stages) to keep HBM busy.
@@ -37,6 +37,7 @@
 
 #include "../coll/bulk_kernels.cuh"
 #include "../proto/dev_backend.cuh"
+#include "oneshot_fused.cuh"
 
 namespace b200ipc {
 
@@ -61,17 +62,15 @@ struct GemmArArgs {
                          // 128-row operand tile then holds other data, which only reaches accumulator rows >= M)
   int mode;              // kGemmModeReduceScatter / kGemmModeOneShot
   uint32_t done_target;  // value the local delivery counter reaches when all owners are done (reduce-scatter)
-  uint32_t epoch;        // launch number of this kernel family on the communicator: flag value, and its parity
-                         // picks the half of the one-shot landing zone
+  uint32_t epoch;        // launch number of this kernel family on the communicator: the flag value
   float eps;
   int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
   // heap offsets (same on every rank)
-  uint64_t landing_off;  // reduce-scatter: [world][rows_per_rank][N]; one-shot: [2][world][M][N]   16-bit partials
-  uint64_t flags_off;    // reduce-scatter: [world][m_tiles][n_tiles][4]; one-shot: [2][world][n_tiles]   uint32
+  uint64_t landing_off;  // reduce-scatter: [world][rows_per_rank][N] partials from every source; one-shot: [M][N], this rank's own
+  uint64_t flags_off;    // reduce-scatter: [world][m_tiles][n_tiles][4]; one-shot: [n_tiles]   uint32
   uint64_t inv_off;      // [M] fp32: 1/rms of every row, written by the row's owner
   uint64_t out_off;      // [M][N]
   uint64_t res_out_off;  // [M][N] (0 = not wanted)
-  uint64_t oneshot_half_bytes;  // size of one half of the one-shot landing zone
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -183,7 +182,9 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
 // Phase time stamps of CTA 0 (global timer, ns), kept in the control region of the heap at
 // kGemmTraceOff: [0] entry, [1] set-up done, [2] last TMA issued, [3] last MMA committed,
 // [4] last epilogue tile stored, [5] tensor memory returned, [6] all deliveries seen,
-// [7] exit.  A debugging and tuning aid; costs a handful of timer reads by single threads.
+// [7] exit, [8] / [9] before / after the flag release of the epilogue warp that holds rows 0..31,
+// [10] one-shot: every tile of the local product is there.
+// A debugging and tuning aid; costs a handful of timer reads by single threads.
 constexpr size_t kGemmTraceOff = 1024;
 __device__ __forceinline__ void gemm_trace(const RankView& me, const HeapLayout& lay, int slot) {
   if (blockIdx.x == 0)
@@ -195,12 +196,15 @@ constexpr int kGemmDoneTotalSlot = 3;   // device-side running total of expected
 constexpr int kGemmDoneSlot = 4;        // the delivery counter the owners' CTAs add to
 constexpr int kGemmEpochSlot = 6;       // device-side running launch number (graph-captured launches)
 
-template <int BN, int STAGES, int A_ROWS>
+// A stage of the ring holds KSUB sub-tiles of 64 columns (one 128-byte swizzle row each) of both
+// operands: KSUB > 1 makes every row of W contribute KSUB x 128 contiguous bytes per stage, which is
+// what a weight-streaming (small M) problem needs from HBM.
+template <int BN, int STAGES, int A_ROWS, int KSUB = 1>
 struct GemmSmem {
-  // The X stages come first: with A_ROWS < 128 the tensor core reads past a stage's rows into the
-  // next stages (and, for the last one, into the W stages), never outside this structure.
-  alignas(1024) unsigned char a[STAGES][A_ROWS * kGemmBK * 2];
-  alignas(1024) unsigned char b[STAGES][BN * kGemmBK * 2];
+  // The X stages come first: with A_ROWS < 128 the tensor core reads past a sub-tile's rows into the
+  // next ones (and, for the last one, into the W stages), never outside this structure.
+  alignas(1024) unsigned char a[STAGES][KSUB][A_ROWS * kGemmBK * 2];
+  alignas(1024) unsigned char b[STAGES][KSUB][BN * kGemmBK * 2];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -209,7 +213,9 @@ struct GemmSmem {
   uint32_t tmem_base;
   int abort_flag;
   int owner_fail;
+  int exchange_abort;
   float red[kGemmThreads / 32];
+  float exchange_part[32];
 };
 static_assert(kGemmBM * kGemmBK * 2 <= 4 * 64 * kGemmBK * 2, "the W stages must cover what a short X stage leaves to read");
 
@@ -292,12 +298,11 @@ struct RowCtx {
     }
     return ok;
   }
-  // One-shot: bounded wait until every source rank has delivered every column tile (of all rows).
-  __device__ bool wait_oneshot_flags(int tid, int nthr) const {
-    const int W = me->world;
-    const uint32_t* base = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off) + size_t(epoch & 1u) * W * n_tiles;
+  // One-shot: bounded wait until every column tile of this rank's own partial product is in memory.
+  __device__ bool wait_local_tiles(int tid, int nthr) const {
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off);
     bool ok = true;
-    for (int f = tid; f < W * n_tiles && ok; f += nthr) ok = poll_flag(base + f, f / n_tiles, f % n_tiles, 23);
+    for (int f = tid; f < n_tiles && ok; f += nthr) ok = poll_flag(base + f, me->rank, f, 23);
     return ok;
   }
 
@@ -400,10 +405,10 @@ struct RowCtx {
   }
 };
 
-template <typename T, int BN, int STAGES, int A_ROWS>
+template <typename T, int BN, int STAGES, int A_ROWS, int KSUB>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_constant__ GemmArArgs args) {
   extern __shared__ unsigned char smem_raw[];
-  using Smem = GemmSmem<BN, STAGES, A_ROWS>;
+  using Smem = GemmSmem<BN, STAGES, A_ROWS, KSUB>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const RankView& me = args.k.v[blockIdx.y];
@@ -416,7 +421,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   const int M = args.M, N = args.N, K = args.K;
   const int m_tiles = (M + kGemmBM - 1) / kGemmBM;
   const int n_tiles = N / BN;
-  const int k_iters = (K + kGemmBK - 1) / kGemmBK;
+  const int k_iters = (K + kGemmBK * KSUB - 1) / (kGemmBK * KSUB);  // columns past K read as zeros
   const int total_tiles = m_tiles * n_tiles;
   const int rpr = args.rows_per_rank;
   const bool oneshot = args.mode == kGemmModeOneShot;
@@ -430,7 +435,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     done_target += ld_volatile_u32(me.seq_dev + kGemmDoneTotalSlot);
   }
   constexpr uint32_t kTmemCols = 2 * BN;
-  const uint32_t stage_bytes = uint32_t(args.a_box_rows + BN) * kGemmBK * 2;
+  const uint32_t stage_bytes = uint32_t(args.a_box_rows + BN) * kGemmBK * 2 * KSUB;
   const bool mute = (me.flags & kMuteSends) != 0;
 
   // ---- set-up ---------------------------------------------------------------------------
@@ -482,8 +487,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, timeout_ns)) break;
           mbar_expect_tx(&s.full[st], stage_bytes);
-          tma_load_2d(s.a[st], ta, &s.full[st], kb * kGemmBK, mt * kGemmBM);
-          tma_load_2d(s.b[st], tb, &s.full[st], kb * kGemmBK, nt * BN);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            tma_load_2d(s.a[st][sub], ta, &s.full[st], (kb * KSUB + sub) * kGemmBK, mt * kGemmBM);
+            tma_load_2d(s.b[st][sub], tb, &s.full[st], (kb * KSUB + sub) * kGemmBK, nt * BN);
+          }
         }
       }
       gemm_trace(me, lay, 2);
@@ -509,12 +517,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&s.full[st], ph, abort_flag, timeout_ns)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st]));
-          const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st]));
 #pragma unroll
-          for (int k = 0; k < kGemmBK / 16; ++k) {
-            // advance 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
-            umma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint64_t da = make_sw128_kmajor_desc(smem_u32(s.a[st][sub]));
+            const uint64_t db = make_sw128_kmajor_desc(smem_u32(s.b[st][sub]));
+#pragma unroll
+            for (int k = 0; k < kGemmBK / 16; ++k) {
+              // advance 16 elements (32 bytes) along K inside the swizzle atom: +2 in 16-byte units
+              umma_f16(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || sub > 0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit(&s.empty[st]);  // the stage may be refilled once these MMAs have read it
         }
@@ -527,7 +538,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     // epilogue warps 2..5: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     const int lane_group = warp & 3;
     uint32_t tile_i = 0;
-    const size_t os_landing = args.landing_off + size_t(epoch & 1u) * args.oneshot_half_bytes;
     for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G, ++tile_i) {
       const int mt = gemm_mtile_at(t / n_tiles, m_tiles, W, rpr), nt = t % n_tiles;
       const uint32_t buf = tile_i & 1u;
@@ -566,12 +576,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
             const int chunk = lane & 7;
             const uint4 o = *reinterpret_cast<const uint4*>(patch + pr * 128 + ((chunk ^ (pr & 7)) * 16));
             const int row = first_row + pr;
-            if (row < M && !mute) {
+            if (row < M && (oneshot || !mute)) {
               const size_t col = size_t(nt) * BN + size_t(c) + size_t(chunk) * 8;
               if (oneshot) {
-                // every rank gets this rank's copy: [source][row][N]
-                const size_t off = os_landing + ((size_t(rank) * M + size_t(row)) * size_t(N) + col) * 2;
-                for (int k = 0; k < W; ++k) *reinterpret_cast<uint4*>(me.peer[(rank + k) % W] + off) = o;
+                // the partial product stays here: [row][N]; the exchange that follows reads it
+                *reinterpret_cast<uint4*>(me.heap + args.landing_off + (size_t(row) * size_t(N) + col) * 2) = o;
               } else {
                 const int owner = row / rpr;
                 char* dst = me.peer[owner] + args.landing_off +
@@ -587,17 +596,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       tc_fence_before_sync();
       __syncwarp();  // also orders this warp's row stores before the flag stores below
       if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
-      if (first_row < M && !mute) {
+      if (lane_group == 0 && lane == 0) gemm_trace(me, lay, 8);
+      if (first_row < M && oneshot) {
+        // one local flag per column tile (rows 0..31 are all there is); device scope is enough, the
+        // reader is another CTA of this kernel
+        if (lane == 0) {
+          uint32_t* f = reinterpret_cast<uint32_t*>(me.heap + args.flags_off) + nt;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+        }
+      } else if (first_row < M && !mute) {
         // st.release.sys orders this warp's row stores (made visible to the storing lane by the
         // __syncwarp above) before the flag; no separate fence
-        if (oneshot) {
-          // one flag per (source, column tile) on every rank; rows 0..31 are all there is
-          if (lane < W) {
-            uint32_t* f = reinterpret_cast<uint32_t*>(me.peer[lane] + args.flags_off) +
-                          (size_t(epoch & 1u) * W + size_t(rank)) * n_tiles + nt;
-            st_release_sys_u32(f, epoch);
-          }
-        } else {
+        {
           // one flag per (source, tile, 32-row group) on every owner that got rows from this warp:
           // no barrier between the epilogue warps is needed, each warp answers for its own rows
           int last_row = first_row + 31;
@@ -610,9 +620,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           }
         }
       }
+      if (lane_group == 0 && lane == 0) gemm_trace(me, lay, 9);
     }
     if (threadIdx.x == 64) gemm_trace(me, lay, 4);
-  } else if (!oneshot) {
+  } else if (oneshot) {
+    // ---- one-shot: these warps have nothing to do until the exchange; they use the time to pull what the
+    // exchange will read (residual row, gamma) into L2 and to warm the address translation of what it
+    // will write, so that the first access after the GEMM is not a cold one -------------------------------
+    if (args.with_norm && int(blockIdx.x) < M) {
+      const int otid = int(threadIdx.x) - (kGemmThreads - kGemmOwnerThreads);
+      const int per = (M + G - 1) / G;
+      const size_t row_bytes = size_t(N) * 2;
+      for (int rr = 0; rr < per; ++rr) {
+        const int row = int(blockIdx.x) * per + rr;
+        if (row >= M) break;
+        const char* res = static_cast<const char*>(args.residual[blockIdx.y]) + size_t(row) * row_bytes;
+        const char* gam = static_cast<const char*>(args.gamma[blockIdx.y]);
+        const char* o1 = me.heap + args.out_off + size_t(row) * row_bytes;
+        const char* o2 = me.heap + args.res_out_off + size_t(row) * row_bytes;
+        for (size_t b = size_t(otid) * 128; b < row_bytes; b += size_t(kGemmOwnerThreads) * 128) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(res + b));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(gam + b));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(o1 + b));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(o2 + b));
+        }
+      }
+    }
+  } else {
     // ---- owner side (warps 6..11), concurrent with the GEMM: one row at a time per CTA, in the order
     // in which the rows complete ----------------------------------------------------------------------
     const int otid = int(threadIdx.x) - (kGemmThreads - kGemmOwnerThreads);
@@ -679,23 +713,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   bool failed = s.owner_fail != 0;
 
   if (oneshot) {
-    // ---- one-shot: every rank adds the world copies of each row, the residual, and normalises -----
-    const size_t os_landing = args.landing_off + size_t(epoch & 1u) * args.oneshot_half_bytes;
-    if (int(blockIdx.x) < M) {
-      rc.wait_oneshot_flags(int(threadIdx.x), nthreads);
+    // ---- one-shot: the CTAs that hold rows exchange them with every rank (flag-in-data), add the world
+    // copies, the residual, and normalise ------------------------------------------------------------
+    if constexpr (A_ROWS <= kGemmOneShotMaxRows) {
+      rc.wait_local_tiles(int(threadIdx.x), nthreads);  // every CTA takes a piece of the product
       __syncthreads();
+      if (threadIdx.x == 0) gemm_trace(me, lay, 10);
       failed = s.owner_fail != 0;
-      for (int row = int(blockIdx.x); row < M && !failed; row += G) {
-        const char* copy0 = me.heap + os_landing + size_t(row) * size_t(N) * 2;
-        float ss = rc.sum_row(copy0, size_t(M) * size_t(N) * 2, row, int(threadIdx.x), nthreads, 1u << rank);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) s.red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < nwarps; ++w) tot += s.red[w];
-        rc.finish_row(row, int(threadIdx.x), nthreads, rsqrtf(tot / float(N) + args.eps));
-        __syncthreads();  // s.red is reused by the next row
+      if (!failed) {
+        RankView v = me;  // the exchange takes its operands the way a launch would hand them over
+        v.in = me.heap + args.landing_off;
+        v.out = me.heap + args.out_off;
+        v.nelems = uint64_t(M) * uint64_t(N);
+        v.aux[0] = reinterpret_cast<uint64_t>(args.residual[blockIdx.y]);
+        v.aux[1] = reinterpret_cast<uint64_t>(args.gamma[blockIdx.y]);
+        v.aux[2] = reinterpret_cast<uint64_t>(me.heap + args.res_out_off);
+        v.aux[3] = uint64_t(uint32_t(N)) | (uint64_t(__float_as_uint(args.with_norm ? args.eps : 1.0f)) << 32);
+        float* part = s.exchange_part;
+        int* ab = &s.exchange_abort;
+        if (args.with_norm) {
+          switch (W) {
+            case 1: oneshot_fused_body<T, T, 1, kEpiNorm>(v, lay, part, ab, false); break;
+            case 2: oneshot_fused_body<T, T, 2, kEpiNorm>(v, lay, part, ab, false); break;
+            case 4: oneshot_fused_body<T, T, 4, kEpiNorm>(v, lay, part, ab, false); break;
+            default: oneshot_fused_body<T, T, 8, kEpiNorm>(v, lay, part, ab, false); break;
+          }
+        } else {
+          switch (W) {
+            case 1: oneshot_fused_body<T, T, 1, kEpiScale>(v, lay, part, ab, false); break;
+            case 2: oneshot_fused_body<T, T, 2, kEpiScale>(v, lay, part, ab, false); break;
+            case 4: oneshot_fused_body<T, T, 4, kEpiScale>(v, lay, part, ab, false); break;
+            default: oneshot_fused_body<T, T, 8, kEpiScale>(v, lay, part, ab, false); break;
+          }
+        }
       }
     }
     if (threadIdx.x == 0) gemm_trace(me, lay, 6);
@@ -761,6 +811,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       __threadfence();
       if (atomicAdd(me.seq_dev + 1, 1u) == gridDim.x - 1) {
         me.seq_dev[1] = 0;
+        me.seq_dev[0] += me.seq_step;  // the one-shot exchange used flag-in-data sequence numbers
         me.seq_dev[kGemmEpochSlot] += 1;
         me.seq_dev[kGemmDoneTotalSlot] += args.done_target;
         __threadfence();
