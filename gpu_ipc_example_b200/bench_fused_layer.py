@@ -9,15 +9,21 @@ M in {1, 16, 128, 2048} (`--rows`); X ~ N(0,1), W ~ N(0,0.02), residual ~ N(0,1)
 Arms (same inputs, 3 rotating weight copies so that small-M cases stream the weight from HBM rather
 than L2).  Every arm is timed twice with CUDA events on the launching stream, max over ranks:
 `*_us` is the eager loop a PyTorch user runs (host launch cost included, which dominates at small M),
-`*_gpu_us` removes the host: the baseline and two_step arms are replayed from a CUDA graph, all three arms are replayed from a CUDA graph of 10 calls (the library keeps its sequence
-numbers on the device for that).
-  fused     this library: one tcgen05/TMA kernel (GEMM + reduce-scatter epilogue + owner reduce +
-            residual + RMSNorm + all-gather)
-  two_step  this library: cuBLAS GEMM, then the one-shot all-reduce fused with residual + RMSNorm
-  baseline  cuBLAS GEMM + NCCL all-reduce + separate add and normalise kernels (plain PyTorch)
+`*_gpu_us` removes the host: all arms are replayed from a CUDA graph of 10 calls (the library keeps
+its sequence numbers on the device for that).
+  fused         this library: one tcgen05/TMA kernel (GEMM + exchange + residual + RMSNorm)
+  fused_packed  the same with the weight packed once by Communicator.pack_weight
+  two_step      this library: cuBLAS GEMM, then the one-shot all-reduce fused with residual + RMSNorm
+  baseline      cuBLAS GEMM + NCCL all-reduce + ONE fused add + RMSNorm step (torch's fused rms_norm
+                kernel after one add kernel): what a tuned PyTorch deployment runs
 Prints one JSON object per M with times, the fraction of the roofline (the slower of FLOPs at the
-measured GEMM peak, NVLink bytes at 770 GB/s per direction and, as a third line, weight bytes at the
-measured HBM rate) and the maximum deviation from an fp32 reference.
+measured GEMM peak and NVLink bytes at 900 GB/s per direction, the nominal link rate; the figure at
+the measured 770 GB/s peer copy is given next to it; as a third line, weight bytes at the measured
+HBM rate) and the maximum deviation from an fp32 reference.
+
+`--ag` times the other fused layer instead: all-gather of row-sharded activations -> column-parallel
+GEMM (`allgather_linear`) against cuBLAS + NCCL all-gather and against this library's all-gather +
+cuBLAS, at K = 8192, N_local = 7168 (the gate-up shard), M in {128, 2048, 8192} by default.
 """
 from __future__ import annotations
 
@@ -49,7 +55,10 @@ def main():
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--dtype", default="fp16")
+    ap.add_argument("--ag", action="store_true", help="time all-gather -> GEMM instead of GEMM -> all-reduce")
     args = ap.parse_args()
+    if args.ag:
+        return main_ag(args)
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -66,7 +75,7 @@ def main():
         comm_g = Communicator.virtual(1, local, staging_bytes=512 << 20, device_seq=True)
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     peak_flops, hbm_bw, peak_src = load_peaks()
-    link_bw = 770e9
+    link_nominal, link_measured = 900e9, 770e9
     K, N = args.k, args.n
     g = torch.Generator(device="cuda").manual_seed(rank)
     ncopy = 3
@@ -163,9 +172,13 @@ def main():
             y = x @ weights[i % ncopy].t()
             if multi:
                 dist.all_reduce(y)
-            s = y + residual
-            v = s.float()
-            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dtype) * gamma, s
+            s = y.add_(residual)
+            return torch.nn.functional.rms_norm(s, (N,), gamma, 1e-5), s
+
+        packed = [Communicator.pack_weight(w) for w in weights]
+
+        def fused_packed_g(i):
+            return comm_g.linear_allreduce(x, packed[i % ncopy], residual, gamma, 1e-5)
 
         # correctness of both library arms against fp32
         parts = [x.float() @ weights[0].float().t()]
@@ -188,6 +201,9 @@ def main():
         t_fused = timed(fused, args.iters)
         t_base = timed(baseline, args.iters)
         g_fused = timed_graph(fused_g, 10)
+        g_packed = timed_graph(fused_packed_g, 10)
+        out_p, _ = fused_packed_g(0)
+        row["max_abs_err_fused_packed"] = round(float((unwrap(out_p).float() - n_ref).abs().max()), 4)
         g_base = timed_graph(baseline, 10)
         g_two = timed_graph(two_step_g, 10) if t_two else None
         comm.check()
@@ -195,7 +211,8 @@ def main():
         flops = 2.0 * M * K * N
         payload = M * N * 2
         link_bytes = 2.0 * (world - 1) / world * payload if multi else 0.0
-        roof = max(flops / peak_flops, link_bytes / link_bw)
+        roof = max(flops / peak_flops, link_bytes / link_nominal)
+        roof_measured_link = max(flops / peak_flops, link_bytes / link_measured)
         t_fused_eager, t_fused = t_fused, g_fused  # fractions below refer to device time
         hbm_floor = (K * N * 2 + M * K * 2) / hbm_bw
         row.update({
@@ -203,12 +220,16 @@ def main():
             "two_step_us": round(t_two * 1e6, 2) if t_two else None,
             "baseline_us": round(t_base * 1e6, 2),
             "fused_gpu_us": round(g_fused * 1e6, 2),
+            "fused_packed_gpu_us": round(g_packed * 1e6, 2),
             "two_step_gpu_us": round(g_two * 1e6, 2) if g_two else None,
             "baseline_gpu_us": round(g_base * 1e6, 2),
             "speedup_vs_baseline": round(t_base / t_fused_eager, 3),
             "speedup_vs_baseline_gpu": round(g_base / g_fused, 3),
             "roofline_us": round(roof * 1e6, 2),
             "roofline_fraction": round(roof / t_fused, 3),
+            "roofline_us_at_measured_link": round(roof_measured_link * 1e6, 2),
+            "roofline_fraction_at_measured_link": round(roof_measured_link / t_fused, 3),
+            "roofline": "max(2MKN / measured cuBLAS burst peak, 2(n-1)/n * M*N*2 B / 900 GB/s nominal link)",
             "weight_stream_floor_us": round(hbm_floor * 1e6, 2),
             "fraction_of_weight_stream_floor": round(hbm_floor / t_fused, 3),
             "fused_tflops": round(flops / t_fused / 1e12, 1),
@@ -221,6 +242,97 @@ def main():
     if multi:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def main_ag(args):
+    """all-gather -> GEMM: X row-sharded [M / world, K] per rank, W_local [N_local, K]; Y = concat(X) @ W_local^T."""
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    multi = world > 1
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        comm = Communicator.from_torch_distributed(local, staging_bytes=1024 << 20, nvls=True)
+    else:
+        comm = Communicator.virtual(1, local, staging_bytes=1024 << 20)
+    dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    peak_flops, hbm_bw, peak_src = load_peaks()
+    K = args.k if args.k != 3584 else 8192
+    N = args.n if args.n != 8192 else 7168
+    rows = args.m if args.m != [1, 16, 128, 2048] else [128, 2048, 8192]
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    ncopy = 3
+    weights = [(torch.randn(N, K, device="cuda", generator=g) * 0.02).to(dtype) for _ in range(ncopy)]
+
+    def reduce_max(v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, iters):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return reduce_max(e0.elapsed_time(e1) / iters * 1e-3)
+
+    for M in rows:
+        M = (M + world - 1) // world * world
+        shard = torch.randn(M // world, K, device="cuda", generator=g).to(dtype)
+        full = torch.empty(M, K, device="cuda", dtype=dtype)
+
+        def fused(i):
+            return comm.allgather_linear(shard, weights[i % ncopy])
+
+        def ours_two_step(i):
+            comm.all_gather(shard, full)
+            return full @ weights[i % ncopy].t()
+
+        def baseline(i):
+            if multi:
+                dist.all_gather_into_tensor(full, shard)
+            else:
+                full.copy_(shard)
+            return full @ weights[i % ncopy].t()
+
+        baseline(0)
+        ref = full.float() @ weights[0].float().t()
+        out = fused(0)
+        out = out[0] if isinstance(out, (list, tuple)) else out
+        err = float((out.float() - ref).abs().max())
+        t_f = timed(fused, args.iters)
+        t_t = timed(ours_two_step, args.iters)
+        t_b = timed(baseline, args.iters)
+        comm.check()
+        flops = 2.0 * M * K * N
+        link_bytes = (world - 1) / world * M * K * 2 if multi else 0.0
+        roof = max(flops / peak_flops, link_bytes / 900e9)
+        row = {"layer": "allgather_linear", "M": M, "K": K, "N_local": N, "world": world, "dtype": args.dtype,
+               "fused_us": round(t_f * 1e6, 2), "ours_allgather_then_cublas_us": round(t_t * 1e6, 2),
+               "nccl_allgather_then_cublas_us": round(t_b * 1e6, 2), "speedup_vs_baseline": round(t_b / t_f, 3),
+               "roofline_us": round(roof * 1e6, 2), "roofline_fraction": round(roof / t_f, 3),
+               "roofline_fraction_at_measured_link": round(max(flops / peak_flops, link_bytes / 770e9) / t_f, 3),
+               "roofline": "max(2MKN / measured cuBLAS burst peak, (n-1)/n * M*K*2 B / 900 GB/s nominal link)",
+               "fused_tflops": round(flops / t_f / 1e12, 1), "max_abs_err_vs_fp32": round(err, 4), "peaks": peak_src,
+               "timing": "launch loop (CUDA events, max over ranks); every arm streams 3 rotating weight copies"}
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    comm.close()
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
 
 
 if __name__ == "__main__":

@@ -112,6 +112,7 @@ def ninja_text(with_torch: bool = True) -> str:
     core_objs.append(cu("fused/fused_ops.cu"))
     core_objs.append(cu("capi/no_alloc.cu"))
     core_objs.append(cu("fused/gemm_ar.cu"))
+    core_objs.append(cu("model/decode_ops.cu"))
 
     lib = f"{PKG}/libb200ipc.so"
     w(f"build {lib}: link_so {' '.join(core_objs)}")

@@ -3,8 +3,11 @@
 #include <algorithm>
 #include <cctype>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
 #include <sstream>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "../common/check.h"
 #include "../proto/wire_format.h"
@@ -29,6 +32,17 @@ const char* sched_name(SchedKind s) {
 }
 
 namespace {
+
+// NVTX range around the host side of a collective (what a timeline tool shows next to the kernel);
+// costs a null check when no tool is attached.
+struct NvtxRange {
+  explicit NvtxRange(const char* what, const AlgoSpec& a, size_t bytes) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "b200ipc::%s[%s:%s] %zu B", what, a.automatic ? "auto" : sched_name(a.sched), proto_name(a.proto), bytes);
+    nvtxRangePushA(buf);
+  }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 struct NamedAlgo {
   const char* name;
@@ -139,6 +153,7 @@ void Comm::common_init(const CommOptions& opt) {
     std::memset(p, 0, sizeof(StatusBlock));
     status_[i] = static_cast<StatusBlock*>(p);
   }
+  if (const char* e = std::getenv("B200IPC_DEBUG")) trace_wires_ = std::atoi(e) != 0;
   if (const char* e = std::getenv("B200IPC_TIMEOUT_US")) {
     long long us = std::atoll(e);
     if (us > 0) timeout_ns_ = uint64_t(us) * 1000ull;
@@ -264,7 +279,7 @@ void Comm::fill_views(KArgs* args, const void* const* ins, void* const* outs, si
     RankView& v = args->v[i];
     v.rank = h.rank();
     v.world = world_;
-    v.flags = flags;
+    v.flags = flags | (trace_wires_ ? uint32_t(kTraceWires) : 0u);
     v.heap = h.base();
     for (int r = 0; r < kMaxRanks; ++r) v.peer[r] = r < world_ ? h.peer(r) : h.base();
     v.mc = h.multicast();
@@ -611,6 +626,7 @@ AlgoSpec Comm::choose_all_reduce(size_t bytes, bool symmetric) const {
 CollInfo Comm::all_reduce(AlgoSpec algo, DType t, const void* const* ins, void* const* outs, size_t nelems,
                           LaunchGeom geom, cudaStream_t stream, uint32_t extra_flags) {
   B200_REQUIRE(nelems > 0, "empty all-reduce");
+  NvtxRange nvtx("all_reduce", algo, nelems * 2);
   B200_CUDA_CHECK(cudaSetDevice(device_));
   if (world_ == 1) {
     if (ins[0] != outs[0]) B200_CUDA_CHECK(cudaMemcpyAsync(outs[0], ins[0], nelems * 2, cudaMemcpyDeviceToDevice, stream));
@@ -641,6 +657,7 @@ CollInfo Comm::all_reduce(AlgoSpec algo, DType t, const void* const* ins, void* 
 CollInfo Comm::all_gather(AlgoSpec algo, DType t, const void* const* ins, void* const* outs, size_t nelems,
                           LaunchGeom geom, cudaStream_t stream, uint32_t extra_flags) {
   B200_REQUIRE(nelems > 0, "empty all-gather");
+  NvtxRange nvtx("all_gather", algo, nelems * 2);
   B200_CUDA_CHECK(cudaSetDevice(device_));
   if (world_ == 1) {
     if (ins[0] != outs[0]) B200_CUDA_CHECK(cudaMemcpyAsync(outs[0], ins[0], nelems * 2, cudaMemcpyDeviceToDevice, stream));
@@ -671,6 +688,7 @@ CollInfo Comm::all_gather(AlgoSpec algo, DType t, const void* const* ins, void* 
 CollInfo Comm::reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, void* const* outs, size_t nelems,
                               LaunchGeom geom, cudaStream_t stream, uint32_t extra_flags) {
   B200_REQUIRE(nelems > 0, "empty reduce-scatter");
+  NvtxRange nvtx("reduce_scatter", algo, nelems * 2);
   B200_CUDA_CHECK(cudaSetDevice(device_));
   if (world_ == 1) {
     if (ins[0] != outs[0]) B200_CUDA_CHECK(cudaMemcpyAsync(outs[0], ins[0], nelems * 2, cudaMemcpyDeviceToDevice, stream));

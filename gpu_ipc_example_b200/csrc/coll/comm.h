@@ -126,6 +126,8 @@ class Comm {
   bool device_seq() const { return device_seq_; }
   void set_seq(uint32_t s) { seq_ = s; }
   uint64_t launches() const { return launches_; }
+  bool trace_wires() const { return trace_wires_; }
+  void set_trace_wires(bool on) { trace_wires_ = on; }
   void set_timeout_ms(uint64_t ms) { timeout_ns_ = ms * 1000000ull; }
   // Host barrier (no-op in a virtual world).
   void host_barrier();
@@ -188,6 +190,7 @@ class Comm {
   uint32_t ag_arrive_ = 0;
   uint32_t ag_launches_ = 0;
   bool device_seq_ = false;
+  bool trace_wires_ = false;  // B200IPC_DEBUG=1: kernels leave a record per completed wait in the trace ring
   uint64_t timeout_ns_ = 2000000000ull;
   int max_ctas_ = 0;
   size_t sym_used_ = 0;

@@ -127,9 +127,12 @@ struct Ctx {
   B200_HD void send(char* dst, const typename B::Msg& m) const {
     if (!muted()) B::send(dst, m);
   }
+  B200_HD bool tracing() const { return (flags & kTraceWires) != 0; }
   B200_HD bool wait(typename B::Msg& m, const char* src, uint32_t flag, int site, int peer,
                     int64_t step) const {
-    return B::wait(waiter, m, src, flag, site, peer, step, rank);
+    if (!B::wait(waiter, m, src, flag, site, peer, step, rank)) return false;
+    if (tracing()) waiter.trace(site, peer, step, flag);
+    return true;
   }
 };
 
@@ -164,8 +167,12 @@ B200_HD bool recv_in_order(const Ctx<B>& c, uint32_t flag, int site, int64_t ste
       return false;
 #pragma unroll
     for (int k = 0; k < CNT; ++k) {
-      if (LO + k == skip) use(LO + k, own);
-      else use(LO + k, m[k]);
+      if (LO + k == skip) {
+        use(LO + k, own);
+      } else {
+        if (c.tracing()) c.waiter.trace(site, peer(LO + k), step, flag);
+        use(LO + k, m[k]);
+      }
     }
     return recv_in_order<B, LO + CNT, HI>(c, flag, site, step, skip, own, src, peer, use);
   }

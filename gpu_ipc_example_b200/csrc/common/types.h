@@ -69,6 +69,7 @@ enum ViewFlags : uint32_t {
   kRoundEachAdd = 1u << 0,  // round the running sum to T after each add (the reference sums in T)
   kMuteSends = 1u << 1,     // fault injection: this rank skips every remote store
   kInPlace = 1u << 2,
+  kTraceWires = 1u << 3,    // debug: every completed wait leaves a time-stamped record in the trace ring
 };
 
 // Byte offsets of the regions inside every rank's symmetric heap.  Identical
@@ -87,7 +88,21 @@ constexpr size_t kCtrlClaimOff = 4;            // uint32: which wire writes this
 constexpr size_t kCtrlSeqOff = 256;            // uint32 {sequence offset, finished-CTA counter, barrier offset, -}
 constexpr size_t kCtrlBarrierOff = 4096;       // uint32 pad[kMaxBarrierCtas][kMaxRanks]
 constexpr int kMaxBarrierCtas = 1024;
+// Debug trace ring (B200IPC_DEBUG=1): uint32 {next index, -, -, -} at kCtrlTraceOff, then
+// kTraceEntries records.  The ring keeps the most recent records; the index keeps counting.
+struct TraceRecord {
+  uint64_t t_ns;     // global timer when the wait completed
+  uint32_t wire;     // warp index of the rank
+  uint32_t site;     // schedule-specific id of the wait (0 scatter sink, 1 gather sink, 2/3 bisect far, 4 one-shot, 5 fused one-shot)
+  uint32_t peer;     // rank that sent the transaction
+  uint32_t step;     // loop iteration of the wire
+  uint32_t flag;     // the sequence flag the transaction carried
+  uint32_t rank;     // this rank
+};
+constexpr size_t kCtrlTraceOff = 65536;
+constexpr uint32_t kTraceEntries = 4096;
 constexpr size_t kCtrlBytes = 2u << 20;
+static_assert(kCtrlTraceOff + 16 + size_t(kTraceEntries) * sizeof(TraceRecord) <= kCtrlBytes, "trace ring must fit the control region");
 
 // Everything one rank's kernel needs.  In the single-GPU emulation of N ranks
 // ("virtual world") one launch carries N of these and blockIdx.y selects one.

@@ -27,6 +27,7 @@ struct HostWaiter {
   uint64_t timeout_ns = 2000000000ull;
   int world = 1;
   int wire = 0;
+  void trace(int, int, int64_t, uint32_t) const {}  // the emulator has a debugger instead
 };
 
 template <ProtoKind K, DType T>

@@ -32,12 +32,14 @@ namespace b200ipc {
 // Row-parallel linear layer fused with its all-reduce (and residual-add + RMSNorm): see gemm_ar.cuh.
 struct GemmArPtrs {
   const void* x;         // [M, K] this rank's activation slice, K contiguous
-  const void* w;         // [N, K] this rank's weight slice (nn.Linear layout), K contiguous
+  const void* w;         // [N, K] this rank's weight slice (nn.Linear layout), K contiguous; or, with packed_kblocks > 0,
+                         // the same weight packed as [N/64][packed_kblocks][64][64] swizzled blocks (pack_weight)
   const void* residual;  // [M, N] or nullptr
   const void* gamma;     // [N] or nullptr
   void* out;             // [M, N] in the symmetric heap
   void* res_out;         // [M, N] in the symmetric heap, or nullptr
   void* workspace;       // gemm_ar_workspace() bytes in the symmetric heap, zeroed once before first use
+  int packed_kblocks = 0;  // 0: w is [N, K]; else the number of 64-column blocks per row block of the packed w
 };
 struct GemmArWorkspace {
   size_t landing_bytes = 0;  // partial products landing here

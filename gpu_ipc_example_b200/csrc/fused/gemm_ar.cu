@@ -12,6 +12,7 @@
 #include "fused_ops.h"
 #include "ag_gemm.cuh"
 #include "gemm_ar.cuh"
+#include "gemm_decode.cuh"
 
 namespace b200ipc {
 namespace {
@@ -21,6 +22,7 @@ constexpr int kStages128 = 6;   // 6 x (16 KiB + 16 KiB) = 192 KiB
 constexpr int kStages64 = 8;    // 8 x (16 KiB +  8 KiB) = 192 KiB
 constexpr int kStagesDecode = 16;  // 16 x (4 KiB + 8 KiB) = 192 KiB: M <= 32, the X stage holds 32 rows
 constexpr int kDecodeRows = 32;
+constexpr int kDecodeMaxSplits = 8;
 
 template <typename T, int BN, int STAGES, int A_ROWS, int KSUB = 1>
 const void* kernel_ptr() {
@@ -89,13 +91,109 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
   const int64_t m_tiles = (M + kGemmBM - 1) / kGemmBM;
   // room for either form of the exchange, so that the choice can change between calls
   const size_t rs_landing = size_t(world) * size_t(rpr) * size_t(N) * 2;
-  const size_t os_landing = M <= kGemmOneShotMaxRows ? size_t(M) * size_t(N) * 2 : 0;
+  const size_t os_landing = M <= kGemmOneShotMaxRows ? size_t(M) * size_t(N) * 4 : 0;  // the decode kernel keeps an fp32 product
   w.landing_bytes = up256(std::max(rs_landing, os_landing));
   const size_t rs_flags = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
-  const size_t os_flags = size_t(N / 64) * sizeof(uint32_t);
+  const size_t os_flags = size_t(N / 64) * 4 * kDecodeMaxSplits * sizeof(uint32_t);
   w.flags_bytes = up256(std::max(rs_flags, os_flags));
   w.inv_bytes = up256(size_t(M) * sizeof(float));
   return w;
+}
+
+// Decode sizes (M <= 32, N a multiple of 128): the swapped-operand, split-K kernel of gemm_decode.cuh.
+static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
+                                  bool with_norm, int ctas_req, cudaStream_t stream) {
+  const int W = comm.world();
+  const void* fn = t == DType::F16 ? reinterpret_cast<const void*>(&gemm_decode_kernel<__half>)
+                                   : reinterpret_cast<const void*>(&gemm_decode_kernel<__nv_bfloat16>);
+  const size_t smem = sizeof(DecodeSmem) + 1024;
+  {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (!g_attr_done.count(fn)) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+      g_attr_done.insert(fn);
+    }
+  }
+  int cap = comm.resident_ctas(reinterpret_cast<KernelFn>(const_cast<void*>(fn)), kGemmThreads, smem);
+  B200_REQUIRE(cap >= 1, "GEMM kernel does not fit on the device");
+  cap = std::min<int>(cap, kMaxOneShotWires / (kGemmThreads / 32));
+  const int64_t tiles = N / kDecTileRows;
+  const int64_t kb_total = (K + kGemmBK - 1) / kGemmBK;
+  // split K until the tiles x splits fill the GPU (every split keeps at least two stages of work)
+  int64_t splits = std::max<int64_t>(1, cap / tiles);
+  splits = std::min<int64_t>(splits, std::min<int64_t>(kDecodeMaxSplits, std::max<int64_t>(1, kb_total / (2 * kDecKSub))));
+  const int64_t units = tiles * splits;
+  int ctas = ctas_req > 0 ? ctas_req : int(std::min<int64_t>(cap, std::max<int64_t>(units, M)));
+  B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs, only " << cap << " can run at once");
+
+  GemmArArgs args;
+  std::memset(&args, 0, sizeof(args));
+  args.mode = kGemmModeOneShot;
+  std::vector<const void*> ins(size_t(comm.nlocal()), nullptr);
+  std::vector<void*> outs(size_t(comm.nlocal()), nullptr);
+  comm.fill_views(&args.k, ins.data(), outs.data(), size_t(M * N), 0);
+  const GemmArWorkspace ws = gemm_ar_workspace(W, M, N);
+  size_t landing_off = SIZE_MAX, out_off = SIZE_MAX, res_off = 0;
+  for (int i = 0; i < comm.nlocal(); ++i) {
+    const GemmArPtrs& p = ptrs[i];
+    const size_t lo = comm.sym_offset_of(p.workspace, i);
+    const size_t oo = comm.sym_offset_of(p.out, i);
+    const size_t ro = p.res_out ? comm.sym_offset_of(p.res_out, i) : 0;
+    B200_REQUIRE(lo != SIZE_MAX && oo != SIZE_MAX && ro != SIZE_MAX,
+                 "workspace, out and res_out must be tensors from the symmetric heap (Communicator.empty)");
+    if (i == 0) {
+      landing_off = lo;
+      out_off = oo;
+      res_off = ro;
+    }
+    B200_REQUIRE(lo == landing_off && oo == out_off && ro == res_off, "symmetric tensors must sit at the same offset on every rank");
+    B200_REQUIRE(lo % 256 == 0 && oo % 16 == 0 && ro % 16 == 0, "symmetric tensors must be 16-byte aligned");
+    if (with_norm) B200_REQUIRE(p.gamma != nullptr && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0, "RMSNorm needs gamma and an aligned residual");
+    encode_2d(&args.tma_a[i], t, p.x, uint64_t(M), uint64_t(K), uint32_t(kDecXRows));
+    if (p.packed_kblocks > 0) {
+      B200_REQUIRE(p.packed_kblocks == ptrs[0].packed_kblocks && int64_t(p.packed_kblocks) * 64 >= K,
+                   "packed weight does not match K (pack it with Communicator.pack_weight)");
+      args.w_packed[i] = p.w;
+      args.packed_kblocks = p.packed_kblocks;
+    } else {
+      B200_REQUIRE(ptrs[0].packed_kblocks == 0, "either every rank's weight is packed or none");
+      encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(kDecTileRows));
+    }
+    args.residual[i] = p.residual;
+    args.gamma[i] = p.gamma;
+  }
+  args.M = int(M);
+  args.N = int(N);
+  args.K = int(K);
+  args.rows_per_rank = int(splits);
+  args.eps = eps;
+  args.with_norm = with_norm ? 1 : 0;
+  args.landing_off = landing_off;
+  args.flags_off = landing_off + ws.landing_bytes;
+  args.inv_off = args.flags_off + ws.flags_bytes;
+  args.out_off = out_off;
+  args.res_out_off = res_off;
+  args.epoch = comm.take_gemm_epoch();
+  const int64_t per = (M + ctas - 1) / ctas;
+  const int64_t steps = ceil_div64(ceil_div64(per * (N / 2), 120), kGemmThreads / 32);
+  const uint32_t adv = uint32_t(steps + 1);
+  const uint32_t first = comm.take_seq(adv);
+  for (int i = 0; i < comm.nlocal(); ++i) {
+    args.k.v[i].seq = first;
+    args.k.v[i].seq_step = adv;
+  }
+  void* params[] = {&args};
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+  CollInfo info;
+  info.sched = SchedKind::OneShot;
+  info.proto = ProtoKind::LL512;
+  info.ctas = ctas;
+  info.warps = kGemmThreads / 32;
+  info.nwires = ctas * kGemmThreads / 32;
+  info.steps = (units + ctas - 1) / ctas;
+  info.first_flag = args.epoch;
+  info.launches = 1;
+  return info;
 }
 
 CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
@@ -107,6 +205,8 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
   const int mode = gemm_mode_for(M, with_norm, ptrs[0].residual != nullptr && ptrs[0].res_out != nullptr);
+  if (mode == kGemmModeOneShot && N % kDecTileRows == 0 && std::getenv("B200IPC_GEMM_NO_SWAP") == nullptr)
+    return fused_gemm_decode(comm, t, ptrs, M, N, K, eps, with_norm, ctas_req, stream);
   // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
   // cut the operand traffic per FLOP for large M.
   const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
@@ -116,7 +216,7 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   const bool h = t == DType::F16;
   if (decode) {
     // sub-tiles per stage (contiguous bytes per weight row and stage = 128 x this); the ring always holds 192 KiB
-    int ksub = 2;
+    int ksub = 4;
     if (const char* e = std::getenv("B200IPC_GEMM_KSUB")) ksub = std::atoi(e);
     if (ksub == 4) {
       fn = h ? kernel_ptr<__half, 64, kStagesDecode / 4, kDecodeRows, 4>() : kernel_ptr<__nv_bfloat16, 64, kStagesDecode / 4, kDecodeRows, 4>();
@@ -187,7 +287,16 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
     B200_REQUIRE(lo % 256 == 0 && oo % 16 == 0 && ro % 16 == 0, "symmetric tensors must be 16-byte aligned");
     if (with_norm) B200_REQUIRE(p.gamma != nullptr, "RMSNorm needs gamma");
     encode_2d(&args.tma_a[i], t, p.x, uint64_t(M), uint64_t(K), uint32_t(a_box));
-    encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(BN));
+    if (p.packed_kblocks > 0) {
+      B200_REQUIRE(p.packed_kblocks == ptrs[0].packed_kblocks && p.packed_kblocks % 4 == 0 && int64_t(p.packed_kblocks) * 64 >= K,
+                   "packed weight does not match K (pack it with Communicator.pack_weight)");
+      B200_REQUIRE((reinterpret_cast<uintptr_t>(p.w) & 15) == 0, "packed weight must be 16-byte aligned");
+      args.w_packed[i] = p.w;
+      args.packed_kblocks = p.packed_kblocks;
+    } else {
+      B200_REQUIRE(ptrs[0].packed_kblocks == 0, "either every rank's weight is packed or none");
+      encode_2d(&args.tma_b[i], t, p.w, uint64_t(N), uint64_t(K), uint32_t(BN));
+    }
     args.residual[i] = p.residual;
     args.gamma[i] = p.gamma;
   }

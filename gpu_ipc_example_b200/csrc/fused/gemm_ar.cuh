@@ -26,7 +26,12 @@
 //     + residual, RMSNorm.  No owner, no all-gather, no system-scope release on the critical path.
 //
 // Small M is a weight-streaming problem: the X stage of the ring shrinks to the rows that
-// exist, which buys a ring deep enough (16 stages) to keep HBM busy.
+// exist, and a stage holds several 64-column sub-tiles, so that every row of W contributes a
+// longer contiguous run per stage.  Best of all is a weight PACKED once at load time
+// (Communicator.pack_weight): [N/64][K/64 padded][64 rows][64 columns], every 64 x 64 block
+// stored exactly as the 128-byte-swizzled shared-memory image the tensor core reads - a stage is
+// then one contiguous bulk copy of 8 KiB per sub-tile, which is what HBM likes most (the
+// [N, K] layout makes a tile 64 separate short runs, one DRAM page each).
 // Every wait is bounded (time limit of the communicator); tensor memory is always returned.
 //
 // No counterpart in the reference.  Baseline: cuBLAS GEMM + NCCL all-reduce + a fused
@@ -56,6 +61,8 @@ struct GemmArArgs {
   alignas(64) CUtensorMap tma_b[kMaxRanks];  // W  [N, K], K contiguous (nn.Linear layout)
   const void* residual[kMaxRanks];           // [M, N] or nullptr
   const void* gamma[kMaxRanks];              // [N] or nullptr
+  const void* w_packed[kMaxRanks];           // W in the tile-packed layout (see below), or nullptr: then tma_b is used
+  int packed_kblocks;                        // 64-column blocks per 64-row block in the packed layout
   int M, N, K;
   int rows_per_rank;
   int a_box_rows;        // rows of X one TMA box brings in: 128, or fewer when M is small (the rest of the
@@ -118,6 +125,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
           smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
+}
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted on an mbarrier.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
@@ -183,7 +197,8 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
 // kGemmTraceOff: [0] entry, [1] set-up done, [2] last TMA issued, [3] last MMA committed,
 // [4] last epilogue tile stored, [5] tensor memory returned, [6] all deliveries seen,
 // [7] exit, [8] / [9] before / after the flag release of the epilogue warp that holds rows 0..31,
-// [10] one-shot: every tile of the local product is there.
+// [10] one-shot: every tile of the local product is there.  Behind them, at +128 bytes, a ring of
+// 16 (entry, exit) pairs indexed by the launch number: the spacing of consecutive launches.
 // A debugging and tuning aid; costs a handful of timer reads by single threads.
 constexpr size_t kGemmTraceOff = 1024;
 __device__ __forceinline__ void gemm_trace(const RankView& me, const HeapLayout& lay, int slot) {
@@ -479,6 +494,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     if (lane == 0) {
       const CUtensorMap* ta = &args.tma_a[blockIdx.y];
       const CUtensorMap* tb = &args.tma_b[blockIdx.y];
+      const char* wp = static_cast<const char*>(args.w_packed[blockIdx.y]);
       uint32_t it = 0;
       for (int t = int(blockIdx.x); t < total_tiles && !*abort_flag; t += G) {
         const int mt = gemm_mtile_at(t / n_tiles, m_tiles, W, rpr), nt = t % n_tiles;
@@ -488,9 +504,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
           if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, timeout_ns)) break;
           mbar_expect_tx(&s.full[st], stage_bytes);
 #pragma unroll
-          for (int sub = 0; sub < KSUB; ++sub) {
+          for (int sub = 0; sub < KSUB; ++sub)
             tma_load_2d(s.a[st][sub], ta, &s.full[st], (kb * KSUB + sub) * kGemmBK, mt * kGemmBM);
-            tma_load_2d(s.b[st][sub], tb, &s.full[st], (kb * KSUB + sub) * kGemmBK, nt * BN);
+          if (wp) {
+            // packed W: block (row block, k block) is 8 KiB; the k blocks of one row block are adjacent
+            constexpr uint32_t kBlk = 64 * kGemmBK * 2;
+#pragma unroll
+            for (int rb = 0; rb < BN / 64; ++rb) {
+              const char* src = wp + (size_t(nt * (BN / 64) + rb) * size_t(args.packed_kblocks) + size_t(kb) * KSUB) * kBlk;
+              if (BN == 64) {
+                bulk_load(s.b[st][0], src, kBlk * KSUB, &s.full[st]);
+              } else {
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub) bulk_load(s.b[st][sub] + rb * kBlk, src + sub * kBlk, kBlk, &s.full[st]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int sub = 0; sub < KSUB; ++sub)
+              tma_load_2d(s.b[st][sub], tb, &s.full[st], (kb * KSUB + sub) * kGemmBK, nt * BN);
           }
         }
       }
@@ -639,10 +671,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
         const char* o1 = me.heap + args.out_off + size_t(row) * row_bytes;
         const char* o2 = me.heap + args.res_out_off + size_t(row) * row_bytes;
         for (size_t b = size_t(otid) * 128; b < row_bytes; b += size_t(kGemmOwnerThreads) * 128) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(res + b));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(gam + b));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(o1 + b));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(o2 + b));
+          // real loads, not prefetches: a prefetch that misses the address translation is dropped
+          (void)ld_volatile_u32(res + b);
+          (void)ld_volatile_u32(gam + b);
+          (void)ld_volatile_u32(o1 + b);
+          (void)ld_volatile_u32(o2 + b);
         }
       }
     }
@@ -721,29 +754,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
       if (threadIdx.x == 0) gemm_trace(me, lay, 10);
       failed = s.owner_fail != 0;
       if (!failed) {
-        RankView v = me;  // the exchange takes its operands the way a launch would hand them over
-        v.in = me.heap + args.landing_off;
-        v.out = me.heap + args.out_off;
-        v.nelems = uint64_t(M) * uint64_t(N);
-        v.aux[0] = reinterpret_cast<uint64_t>(args.residual[blockIdx.y]);
-        v.aux[1] = reinterpret_cast<uint64_t>(args.gamma[blockIdx.y]);
-        v.aux[2] = reinterpret_cast<uint64_t>(me.heap + args.res_out_off);
-        v.aux[3] = uint64_t(uint32_t(N)) | (uint64_t(__float_as_uint(args.with_norm ? args.eps : 1.0f)) << 32);
+        FusedOperands op;
+        op.in = me.heap + args.landing_off;
+        op.out = me.heap + args.out_off;
+        op.residual = args.residual[blockIdx.y];
+        op.gamma = args.gamma[blockIdx.y];
+        op.res_out = me.heap + args.res_out_off;
+        op.nelems = uint64_t(M) * uint64_t(N);
+        op.hidden = N;
+        op.scale_or_eps = args.with_norm ? args.eps : 1.0f;
         float* part = s.exchange_part;
         int* ab = &s.exchange_abort;
         if (args.with_norm) {
           switch (W) {
-            case 1: oneshot_fused_body<T, T, 1, kEpiNorm>(v, lay, part, ab, false); break;
-            case 2: oneshot_fused_body<T, T, 2, kEpiNorm>(v, lay, part, ab, false); break;
-            case 4: oneshot_fused_body<T, T, 4, kEpiNorm>(v, lay, part, ab, false); break;
-            default: oneshot_fused_body<T, T, 8, kEpiNorm>(v, lay, part, ab, false); break;
+            case 1: oneshot_fused_body<T, T, 1, kEpiNorm>(me, lay, op, part, ab, false); break;
+            case 2: oneshot_fused_body<T, T, 2, kEpiNorm>(me, lay, op, part, ab, false); break;
+            case 4: oneshot_fused_body<T, T, 4, kEpiNorm>(me, lay, op, part, ab, false); break;
+            default: oneshot_fused_body<T, T, 8, kEpiNorm>(me, lay, op, part, ab, false); break;
           }
         } else {
           switch (W) {
-            case 1: oneshot_fused_body<T, T, 1, kEpiScale>(v, lay, part, ab, false); break;
-            case 2: oneshot_fused_body<T, T, 2, kEpiScale>(v, lay, part, ab, false); break;
-            case 4: oneshot_fused_body<T, T, 4, kEpiScale>(v, lay, part, ab, false); break;
-            default: oneshot_fused_body<T, T, 8, kEpiScale>(v, lay, part, ab, false); break;
+            case 1: oneshot_fused_body<T, T, 1, kEpiScale>(me, lay, op, part, ab, false); break;
+            case 2: oneshot_fused_body<T, T, 2, kEpiScale>(me, lay, op, part, ab, false); break;
+            case 4: oneshot_fused_body<T, T, 4, kEpiScale>(me, lay, op, part, ab, false); break;
+            default: oneshot_fused_body<T, T, 8, kEpiScale>(me, lay, op, part, ab, false); break;
           }
         }
       }
@@ -804,6 +838,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
     }
   }
   if (threadIdx.x == 0) gemm_trace(me, lay, 7);
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    unsigned long long* ring = reinterpret_cast<unsigned long long*>(me.heap + lay.ctrl_off + kGemmTraceOff + 128) + (epoch & 15u) * 2;
+    ring[0] = reinterpret_cast<unsigned long long*>(me.heap + lay.ctrl_off + kGemmTraceOff)[0];
+    ring[1] = globaltimer_ns();
+  }
   if (me.seq_dev) {
     // the last CTA to leave advances the device-side launch number and delivery total
     __syncthreads();

@@ -25,15 +25,28 @@ constexpr int kFusedMaxThreads = 512;  // 16 warps: leaves 128 registers per thr
 template <typename Tout>
 __device__ __forceinline__ uint32_t pack_out(float a, float b) { return Cvt<Tout>::down(a, b); }
 
-// The whole exchange + epilogue for the calling CTA (all its threads call it).  `me` carries the
-// operands as the kernel's launch arguments do: in / out / nelems, aux[0] residual, aux[1] gamma,
-// aux[2] residual_out, aux[3] = hidden | (float bits of eps or scale) << 32.  Written as a function
+// What the exchange works on (by value: the fields sit in registers, not behind a parameter-space
+// or local-memory access on the critical path).
+struct FusedOperands {
+  const void* in;        // [rows, hidden] partial activations of this rank (or the fp32 accumulation buffer)
+  void* out;             // normalised / scaled result
+  const void* residual;  // kEpiNorm
+  const void* gamma;     // kEpiNorm
+  void* res_out;         // kEpiNorm: sum + residual
+  uint64_t nelems;       // rows * hidden
+  int hidden;            // row length (kEpiNorm)
+  float scale_or_eps;    // kEpiScale: multiplier; kEpiNorm: epsilon
+};
+
+// The whole exchange + epilogue for the calling CTA (all its threads call it).  Written as a function
 // so that a kernel that PRODUCES the partial activations (the fused GEMM at decode sizes) can run
 // the same exchange on them without leaving the kernel; such a caller advances the device-side
 // sequence words itself (`advance_seq_dev` false).
-template <typename T, typename Tout, int N, int EPI>
-__device__ __forceinline__ void oneshot_fused_body(const RankView& me, const HeapLayout& lay, float* s_part, int* s_abort_p,
-                                                   bool advance_seq_dev) {
+// F32IN: `me.in` is an fp32 accumulation buffer (several CTAs of the producing kernel have added their
+// shares into it); the exchange rounds what it reads to T and leaves zeros behind for the next launch.
+template <typename T, typename Tout, int N, int EPI, bool F32IN = false>
+__device__ __forceinline__ void oneshot_fused_body(const RankView& me, const HeapLayout& lay, const FusedOperands op,
+                                                   float* s_part, int* s_abort_p, bool advance_seq_dev) {
   using B = DevBackend<ProtoKind::LL512, T>;
   int& s_abort = *s_abort_p;
   const int r = me.rank;
@@ -50,16 +63,15 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   waiter.ctrl_off = lay.ctrl_off;
   waiter.wire = wire;
 
-  const uint32_t* in = static_cast<const uint32_t*>(me.in);
-  const int64_t total_dw = int64_t(me.nelems / 2);
+  const uint32_t* in = static_cast<const uint32_t*>(op.in);
+  const int64_t total_dw = int64_t(op.nelems / 2);
 
   // This CTA's range of dwords [d0, d1).
   int64_t d0, d1;
   int row0 = 0, nrows = 0;
   int64_t row_dw = 0;
   if (EPI == kEpiNorm) {
-    const int hidden = int(uint32_t(me.aux[3]));
-    row_dw = hidden / 2;
+    row_dw = op.hidden / 2;
     const int rows = int(total_dw / row_dw);
     const int per = (rows + int(gridDim.x) - 1) / int(gridDim.x);
     row0 = int(blockIdx.x) * per;
@@ -77,13 +89,51 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   }
   const int64_t ntx = ceil_div64(d1 - d0, B::kPayloadDw);
 
+  // This wire's share of the input, in payload order (what B::load gives for a 16-bit buffer).  With an
+  // fp32 accumulation buffer the raw loads are issued first (load_in_issue) and turned into 16-bit pairs
+  // later (load_in_finish), so that the loads of several transactions overlap.
+  struct RawIn { float4 lo, hi; };
+  auto load_in_issue = [&](typename B::Msg& v, RawIn& raw, int64_t dw) {
+    if constexpr (!F32IN) {
+      B::load(v, in, dw, d1, -1);
+    } else {
+      // lane l holds dwords dw + 4l .. + 3 = 8 accumulated floats; ranges are cut on multiples of four dwords
+      const int64_t i = dw + 4 * lane;
+      raw.lo = raw.hi = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (lane < 30 && i + 4 <= d1) {
+        const float* acc32 = reinterpret_cast<const float*>(op.in) + 2 * i;
+        asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(raw.lo.x), "=f"(raw.lo.y), "=f"(raw.lo.z), "=f"(raw.lo.w) : "l"(acc32) : "memory");
+        asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(raw.hi.x), "=f"(raw.hi.y), "=f"(raw.hi.z), "=f"(raw.hi.w) : "l"(acc32 + 4) : "memory");
+      }
+    }
+  };
+  auto load_in_finish = [&](typename B::Msg& v, const RawIn& raw, int64_t dw) {
+    if constexpr (F32IN) {
+      const int64_t i = dw + 4 * lane;
+      v.d[0] = Cvt<T>::down(raw.lo.x, raw.lo.y);
+      v.d[1] = Cvt<T>::down(raw.lo.z, raw.lo.w);
+      v.d[2] = Cvt<T>::down(raw.hi.x, raw.hi.y);
+      v.d[3] = Cvt<T>::down(raw.hi.z, raw.hi.w);
+      if (lane < 30 && i + 4 <= d1) {  // zeros for the next launch's additions
+        float* acc32 = const_cast<float*>(reinterpret_cast<const float*>(op.in)) + 2 * i;
+        *reinterpret_cast<float4*>(acc32) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(acc32 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  };
+  auto load_in = [&](typename B::Msg& v, int64_t dw) {
+    RawIn raw;
+    load_in_issue(v, raw, dw);
+    load_in_finish(v, raw, dw);
+  };
+
   if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
 
-  const uint32_t* residual = reinterpret_cast<const uint32_t*>(me.aux[0]);
-  uint32_t* res_out = reinterpret_cast<uint32_t*>(me.aux[2]);
-  uint32_t* out = static_cast<uint32_t*>(me.out);
-  const float scale = __uint_as_float(uint32_t(me.aux[3] >> 32));  // kEpiScale: multiplier; kEpiNorm: eps
+  const uint32_t* residual = static_cast<const uint32_t*>(op.residual);
+  uint32_t* res_out = static_cast<uint32_t*>(op.res_out);
+  uint32_t* out = static_cast<uint32_t*>(op.out);
+  const float scale = op.scale_or_eps;  // kEpiScale: multiplier; kEpiNorm: eps
 
   auto slot_at = [&](char* heap, int src, uint32_t flag) {
     return heap + lay.oneshot_off +
@@ -92,6 +142,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   Ctx<B> cx{};
   cx.waiter = waiter;
   cx.rank = r;
+  cx.flags = me.flags;
   const int64_t steps = ceil_div64(ntx, warps);  // transactions per warp, the same on every warp up to one
   bool ok = true;
 
@@ -102,14 +153,26 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   const bool fast = steps <= KMAX;
   if (fast) {
     typename B::Msg own[KMAX], rsd[KMAX], gam[KMAX];
+    RawIn raw[KMAX];
     const bool norm_in_regs = EPI == kEpiNorm && nrows == 1;
+    // every load this warp will need is issued before the first value is used
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      const int64_t j = warp + int64_t(k) * warps;
+      if (j >= ntx) continue;
+      const int64_t dw = d0 + j * B::kPayloadDw;
+      load_in_issue(own[k], raw[k], dw);
+      if (EPI == kEpiNorm) {
+        B::load(rsd[k], residual, dw, d1, -1);
+        if (norm_in_regs) B::load(gam[k], static_cast<const uint32_t*>(op.gamma), dw - d0, row_dw, -1);
+      }
+    }
 #pragma unroll
     for (int k = 0; k < KMAX; ++k) {
       const int64_t j = warp + int64_t(k) * warps;
       if (j >= ntx) continue;
       const uint32_t flag = seq + uint32_t(k);
-      const int64_t dw = d0 + j * B::kPayloadDw;
-      B::load(own[k], in, dw, d1, -1);
+      load_in_finish(own[k], raw[k], d0 + j * B::kPayloadDw);
       B::shuffle(own[k]);
       if (N > 1) {
         B::set_flags(own[k], flag);
@@ -118,17 +181,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
           for (int i = 1; i < N; ++i) B::send(slot_at(me.peer[(r + i) % N], r, flag), own[k]);
         }
       }
-    }
-    if (EPI == kEpiNorm) {
-#pragma unroll
-      for (int k = 0; k < KMAX; ++k) {
-        const int64_t j = warp + int64_t(k) * warps;
-        if (j >= ntx) continue;
-        const int64_t dw = d0 + j * B::kPayloadDw;
-        B::load(rsd[k], residual, dw, d1, -1);
-        B::shuffle(rsd[k]);
-        if (norm_in_regs) B::load(gam[k], reinterpret_cast<const uint32_t*>(me.aux[1]), dw - d0, row_dw, -1);
-      }
+      if (EPI == kEpiNorm) B::shuffle(rsd[k]);
     }
     float ss = 0.f;
 #pragma unroll
@@ -179,7 +232,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
       if (s_abort == 0) {
         float tot = 0.f;
         for (int w = 0; w < warps; ++w) tot += s_part[w];
-        const float inv = rsqrtf(tot / float(int(uint32_t(me.aux[3]))) + scale);
+        const float inv = rsqrtf(tot / float(op.hidden) + scale);
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) {
           const int64_t j = warp + int64_t(k) * warps;
@@ -205,7 +258,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
       const uint32_t flag = seq + uint32_t(k);
       const int64_t dw = d0 + j * B::kPayloadDw;
       typename B::Msg v;
-      B::load(v, in, dw, d1, -1);
+      load_in(v, dw);
       B::shuffle(v);
       if (N > 1) {
         B::set_flags(v, flag);
@@ -248,9 +301,9 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   }
 
   if (EPI == kEpiNorm && s_abort == 0 && !(fast && nrows == 1)) {
-    const int hidden = int(uint32_t(me.aux[3]));
+    const int hidden = op.hidden;
     const float eps = scale;
-    const uint4* gamma = reinterpret_cast<const uint4*>(me.aux[1]);
+    const uint4* gamma = static_cast<const uint4*>(op.gamma);
     const int row_vec = hidden / 8;
     // The row statistic is taken from the rounded sums this CTA has just written, by a reduction whose
     // order depends on nothing but the thread index: every rank computes the same bits (a floating-point
@@ -310,7 +363,17 @@ template <typename T, typename Tout, int N, int EPI>
 __global__ void __launch_bounds__(kFusedMaxThreads) oneshot_fused_kernel(const __grid_constant__ KArgs args) {
   __shared__ float s_part[32];
   __shared__ int s_abort;
-  oneshot_fused_body<T, Tout, N, EPI>(args.v[blockIdx.y], args.lay, s_part, &s_abort, true);
+  const RankView& me = args.v[blockIdx.y];
+  FusedOperands op;
+  op.in = me.in;
+  op.out = me.out;
+  op.residual = reinterpret_cast<const void*>(me.aux[0]);
+  op.gamma = reinterpret_cast<const void*>(me.aux[1]);
+  op.res_out = reinterpret_cast<void*>(me.aux[2]);
+  op.nelems = me.nelems;
+  op.hidden = int(uint32_t(me.aux[3]));
+  op.scale_or_eps = __uint_as_float(uint32_t(me.aux[3] >> 32));
+  oneshot_fused_body<T, Tout, N, EPI>(me, args.lay, op, s_part, &s_abort, true);
 }
 
 }  // namespace b200ipc

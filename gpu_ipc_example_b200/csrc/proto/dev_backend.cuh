@@ -74,6 +74,22 @@ struct DevWaiter {
   const RankView* me;  // kernel parameter space
   size_t ctrl_off;
   int wire;
+  // One record into the rank's trace ring (lane 0 of the calling warp); the device analogue of the
+  // reference's verbose build, which printf's every wire's offsets and message words
+  // (allreduce.hpp:96-101, sequential_transmit.hpp:118-124, 305-331).
+  __device__ void trace(int site, int peer, int64_t step, uint32_t flag) const {
+    if ((threadIdx.x & 31) != 0) return;
+    char* base = me->heap + ctrl_off + kCtrlTraceOff;
+    const uint32_t idx = atomicAdd(reinterpret_cast<uint32_t*>(base), 1u) % kTraceEntries;
+    TraceRecord* r = reinterpret_cast<TraceRecord*>(base + 16) + idx;
+    r->t_ns = globaltimer_ns();
+    r->wire = uint32_t(wire);
+    r->site = uint32_t(site);
+    r->peer = uint32_t(peer);
+    r->step = uint32_t(step);
+    r->flag = flag;
+    r->rank = uint32_t(me->rank);
+  }
   __device__ uint32_t* abort_word() const {
     return reinterpret_cast<uint32_t*>(me->heap + ctrl_off + kCtrlAbortOff);
   }

@@ -25,6 +25,7 @@
 #include "../coll/comm.h"
 #include "../common/check.h"
 #include "../fused/fused_ops.h"
+#include "../model/decode_ops.h"
 
 namespace {
 
@@ -280,9 +281,16 @@ std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::T
   if (!residuals.empty()) check_tensors(c, residuals, "residual");
   if (!gammas.empty()) check_tensors(c, gammas, "gamma");
   if (!res_outs.empty()) check_tensors(c, res_outs, "residual output");
-  TORCH_CHECK(xs[0].dim() == 2 && ws[0].dim() == 2, "b200ipc: x must be [M, K] and weight [N, K]");
-  const int64_t M = xs[0].size(0), K = xs[0].size(1), N = ws[0].size(0);
-  TORCH_CHECK(ws[0].size(1) == K, "b200ipc: weight must be [N, K] with the same K as x");
+  // weight: [N, K], or packed by pack_weight as [N / 64, K blocks, 64, 64]
+  const bool packed = ws[0].dim() == 4;
+  TORCH_CHECK(xs[0].dim() == 2 && (ws[0].dim() == 2 || packed), "b200ipc: x must be [M, K] and weight [N, K] (or packed)");
+  const int64_t M = xs[0].size(0), K = xs[0].size(1), N = packed ? ws[0].size(0) * 64 : ws[0].size(0);
+  if (packed) {
+    TORCH_CHECK(ws[0].size(2) == 64 && ws[0].size(3) == 64 && ws[0].size(1) * 64 >= K && ws[0].size(1) % 4 == 0,
+                "b200ipc: packed weight must be [N / 64, K blocks, 64, 64] covering K");
+  } else {
+    TORCH_CHECK(ws[0].size(1) == K, "b200ipc: weight must be [N, K] with the same K as x");
+  }
   GemmArWorkspace need = gemm_ar_workspace(c.world(), M, N);
   std::vector<GemmArPtrs> p(size_t(c.nlocal()));
   for (int i = 0; i < c.nlocal(); ++i) {
@@ -298,6 +306,7 @@ std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::T
     p[size_t(i)].out = outs[i].data_ptr();
     p[size_t(i)].res_out = res_outs.empty() ? nullptr : res_outs[i].data_ptr();
     p[size_t(i)].workspace = workspaces[i].data_ptr();
+    p[size_t(i)].packed_kblocks = packed ? int(ws[i].size(1)) : 0;
   }
   c10::cuda::CUDAGuard guard(c.device());
   CollInfo info = fused_gemm_allreduce(c, dtype_of(xs[0]), p.data(), M, N, K, float(eps), with_norm, int(ctas),
@@ -330,6 +339,60 @@ std::vector<int64_t> fused_ag_gemm(std::vector<at::Tensor> xs, std::vector<at::T
   return info_vec(info);
 }
 
+// ---- decode-step kernels (model/decode_ops.cu) --------------------------------------------------------
+int sm_count_of(int device) {
+  int n = 0;
+  B200_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
+  return n;
+}
+
+// qkv [B, (hq + 2 hkv) * D] (q rotated in place), caches [B, hkv, max_ctx, D] (k, v of `pos` written).
+void rope_kv_append_op(at::Tensor qkv, at::Tensor kcache, at::Tensor vcache, int64_t hq, int64_t hkv, int64_t pos, double theta) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() && kcache.is_contiguous() && vcache.is_contiguous() && kcache.dim() == 4,
+              "b200ipc: rope_kv_append takes contiguous CUDA tensors, caches [B, hkv, max_ctx, D]");
+  const int64_t B = qkv.size(0), D = kcache.size(3);
+  TORCH_CHECK(qkv.size(1) == (hq + 2 * hkv) * D && kcache.size(0) == B && kcache.size(1) == hkv && vcache.sizes() == kcache.sizes(),
+              "b200ipc: rope_kv_append shape mismatch");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  rope_kv_append(dtype_of(qkv), qkv.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), int(B), int(hq), int(hkv), int(D),
+                 int(kcache.size(2)), int(pos), float(theta), at::cuda::getCurrentCUDAStream(qkv.get_device()));
+}
+
+int64_t attention_splits(int64_t batch, int64_t hkv, int64_t ctx, int64_t device) {
+  return decode_attention_splits(int(batch), int(hkv), int(ctx), sm_count_of(int(device)));
+}
+int64_t attention_workspace_bytes(int64_t batch, int64_t hq, int64_t hkv, int64_t splits) {
+  return int64_t(decode_attention_workspace_bytes(int(batch), int(hq), int(hkv), int(splits)));
+}
+
+// q = the first hq * D columns of qkv [B, (hq + 2 hkv) * D]; returns [B, hq * D].
+at::Tensor decode_attention_op(at::Tensor qkv, at::Tensor kcache, at::Tensor vcache, at::Tensor workspace, int64_t hq, int64_t hkv,
+                               int64_t ctx, int64_t splits) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() && kcache.is_contiguous() && vcache.is_contiguous() && kcache.dim() == 4,
+              "b200ipc: decode_attention takes contiguous CUDA tensors, caches [B, hkv, max_ctx, D]");
+  const int64_t B = qkv.size(0), D = kcache.size(3);
+  TORCH_CHECK(int64_t(workspace.numel() * workspace.element_size()) >= attention_workspace_bytes(B, hq, hkv, splits),
+              "b200ipc: attention workspace too small");
+  at::Tensor out = at::empty({B, hq * D}, qkv.options());
+  c10::cuda::CUDAGuard guard(qkv.device());
+  decode_attention(dtype_of(qkv), qkv.data_ptr(), int(qkv.size(1)), kcache.data_ptr(), vcache.data_ptr(), out.data_ptr(),
+                   workspace.data_ptr(), int(B), int(hq), int(hkv), int(D), int(kcache.size(2)), int(ctx), int(splits),
+                   at::cuda::getCurrentCUDAStream(qkv.get_device()));
+  return out;
+}
+
+// [rows, 2 F] -> [rows, F]: silu(first half) * second half
+at::Tensor silu_mul_op(at::Tensor gate_up) {
+  TORCH_CHECK(gate_up.is_cuda() && gate_up.is_contiguous() && gate_up.dim() == 2 && gate_up.size(1) % 16 == 0,
+              "b200ipc: silu_mul takes a contiguous [rows, 2 F] CUDA tensor, F a multiple of 8");
+  const int64_t rows = gate_up.size(0), F = gate_up.size(1) / 2;
+  at::Tensor act = at::empty({rows, F}, gate_up.options());
+  c10::cuda::CUDAGuard guard(gate_up.device());
+  silu_mul(dtype_of(gate_up), gate_up.data_ptr(), act.data_ptr(), rows, int(F), sm_count_of(gate_up.get_device()),
+           at::cuda::getCurrentCUDAStream(gate_up.get_device()));
+  return act;
+}
+
 int64_t gemm_ar_workspace_bytes(int64_t world, int64_t M, int64_t N) { return int64_t(gemm_ar_workspace(int(world), M, N).total()); }
 
 }  // namespace
@@ -349,6 +412,10 @@ TORCH_LIBRARY(b200ipc, m) {
       "int comm, int ctas) -> int[]",
       &fused_ar_rmsnorm);
   m.def("fused_ar_scale_cast(Tensor[] ins, Tensor[] outs, float scale, int comm, int ctas) -> int[]", &fused_ar_scale_cast);
+  m.def("rope_kv_append(Tensor(a!) qkv, Tensor(b!) kcache, Tensor(c!) vcache, int hq, int hkv, int pos, float theta) -> ()", &rope_kv_append_op);
+  m.def("decode_attention(Tensor qkv, Tensor kcache, Tensor vcache, Tensor(a!) workspace, int hq, int hkv, int ctx, int splits) -> Tensor",
+        &decode_attention_op);
+  m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul_op);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -381,6 +448,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     get(id).heap(int(local)).dump(size_t(offset), size_t(bytes), t.data_ptr());
     return t;
   });
+  m.def("set_trace_wires", [](int64_t id, bool on) { get(id).set_trace_wires(on); });
+  m.def("trace_wires", [](int64_t id) { return get(id).trace_wires(); });
+  // (offset of the trace ring inside the heap, number of records it holds, bytes per record)
+  m.def("trace_ring", [](int64_t id) {
+    const HeapLayout& l = get(id).heap(0).layout();
+    return std::vector<int64_t>{int64_t(l.ctrl_off + kCtrlTraceOff), int64_t(kTraceEntries), int64_t(sizeof(TraceRecord))};
+  });
   m.def("heap_layout", [](int64_t id) {
     const HeapLayout& l = get(id).heap(0).layout();
     return std::vector<int64_t>{int64_t(l.ctrl_off),     int64_t(l.half_off[0]),  int64_t(l.half_off[1]),
@@ -388,6 +462,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                 int64_t(l.staging_off),  int64_t(l.staging_bytes), int64_t(l.total_bytes)};
   });
   m.def("gemm_ar_workspace_bytes", &gemm_ar_workspace_bytes);
+  m.def("attention_splits", &attention_splits);
+  m.def("attention_workspace_bytes", &attention_workspace_bytes);
   m.def("algo_names", &algo_names_help);
   // Parses an algorithm name: (known, is_allgather, automatic, schedule, proto, direct).
   m.def("parse_algo", [](const std::string& name) {

@@ -14,6 +14,11 @@ three ways (`fusion=`):
                (`Communicator.allreduce_residual_rmsnorm`)
   "nccl"       the baseline: cuBLAS projection, `torch.distributed.all_reduce`, separate add and norm
 
+What lies between the GEMMs and the collectives runs in three hand-written kernels when the head
+dimension is 128 (`kernels=True`, the default there): rotary embedding fused with the KV-cache append,
+attention of the new token over the cache (grouped-query, split over the context), SiLU(gate) * up.
+With `kernels=False` the same steps are plain PyTorch ops (the reference path of the tests).
+
 The reference has no model code; its smoke script all-reduces decode-sized fp16 activations the way a
 tensor-parallel decoder does (script/gpu_inference_test.py:29-45).  Weights are random N(0, 0.02).
 """
@@ -48,6 +53,11 @@ class LlamaConfig:
     def tiny(cls) -> "LlamaConfig":
         return cls(layers=2, hidden=512, n_heads=8, n_kv_heads=8, head_dim=64, ffn=1024, vocab=2048)
 
+    @classmethod
+    def tiny128(cls) -> "LlamaConfig":
+        """Small, but with the 70B model's head dimension and grouped-query ratio (the hand-written decode kernels)."""
+        return cls(layers=2, hidden=1024, n_heads=16, n_kv_heads=8, head_dim=128, ffn=2048, vocab=2048)
+
 
 def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
     v = x.float()
@@ -67,9 +77,12 @@ def apply_rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor
 
 class LlamaTP:
     def __init__(self, cfg: LlamaConfig, comm, batch: int, max_ctx: int, fusion: str = "allreduce", seed: int = 0,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, kernels: Optional[bool] = None, pack_weights: bool = False):
         assert fusion in ("gemm", "allreduce", "nccl")
         self.cfg, self.comm, self.fusion = cfg, comm, fusion
+        # the decode kernels are written for head_dim 128 and 1/2/4/8 query heads per KV head
+        can = cfg.head_dim == 128 and (cfg.n_heads // cfg.n_kv_heads) in (1, 2, 4, 8) and cfg.ffn % 8 == 0
+        self.kernels = can if kernels is None else (kernels and can)
         self.world = comm.world if comm is not None else 1
         self.nlocal = comm.nlocal if comm is not None else 1
         self.ranks = [comm._C.rank(comm._h, i) for i in range(self.nlocal)] if comm is not None else [0]
@@ -101,6 +114,22 @@ class LlamaTP:
             self.kcache.append([torch.zeros(batch, self.hkv, max_ctx, D, device=dev, dtype=dt) for _ in range(cfg.layers)])
             self.vcache.append([torch.zeros(batch, self.hkv, max_ctx, D, device=dev, dtype=dt) for _ in range(cfg.layers)])
         self.pos = 0
+        if self.kernels:
+            from .._ext import load
+
+            C = load()
+            dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+            self.attn_splits = C.attention_splits(batch, self.hkv, max_ctx, dev_index)
+            nbytes = C.attention_workspace_bytes(batch, self.hq, self.hkv, self.attn_splits)
+            self.attn_ws = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(self.nlocal)]
+        if pack_weights and fusion == "gemm":
+            # row-parallel weights in the layout the fused GEMM streams fastest (done once, at load time)
+            from ..parallel.communicator import Communicator
+
+            self.wo_run = [[Communicator.pack_weight(w) for w in ws] for ws in self.wo]
+            self.wdown_run = [[Communicator.pack_weight(w) for w in ws] for ws in self.wdown]
+        else:
+            self.wo_run, self.wdown_run = self.wo, self.wdown
 
     # ------------------------------------------------------------------ collectives
     def _reduce_norm(self, residual: List[torch.Tensor], gamma: torch.Tensor, x: List[torch.Tensor], w: List[torch.Tensor]):
@@ -116,6 +145,7 @@ class LlamaTP:
             out, res = (out, res) if isinstance(out, list) else ([out], [res])
             # the kernel's output buffers are reused by the next call of the same shape: hand out copies
             return [o.clone() for o in out], [r.clone() for r in res]
+        assert w[0].dim() == 2, "packed weights are for fusion='gemm'"
         parts = [xi @ wi.t() for xi, wi in zip(x, w)]
         if self.fusion == "allreduce":
             out, res = self.comm.allreduce_residual_rmsnorm(parts if self.nlocal > 1 else parts[0],
@@ -143,6 +173,11 @@ class LlamaTP:
             attn_out = []
             for i in range(self.nlocal):
                 qkv = normed[i] @ self.wqkv[i][l].t()
+                if self.kernels:
+                    torch.ops.b200ipc.rope_kv_append(qkv, self.kcache[i][l], self.vcache[i][l], self.hq, self.hkv, pos, cfg.rope_theta)
+                    attn_out.append(torch.ops.b200ipc.decode_attention(qkv, self.kcache[i][l], self.vcache[i][l], self.attn_ws[i],
+                                                                       self.hq, self.hkv, pos + 1, self.attn_splits))
+                    continue
                 q, k, v = qkv.split([self.hq * D, self.hkv * D, self.hkv * D], dim=-1)
                 q = apply_rope(q.view(B, self.hq, D), posv, cfg.rope_theta)
                 k = apply_rope(k.view(B, self.hkv, D), posv, cfg.rope_theta)
@@ -152,14 +187,17 @@ class LlamaTP:
                 vv = self.vcache[i][l][:, :, :pos + 1]
                 o = F.scaled_dot_product_attention(q.unsqueeze(2), kk, vv, enable_gqa=self.hq != self.hkv)  # [B, hq, 1, D]
                 attn_out.append(o.reshape(B, self.hq * D))
-            normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo[i][l] for i in range(self.nlocal)])
+            normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo_run[i][l] for i in range(self.nlocal)])
             act = []
             for i in range(self.nlocal):
                 gu = normed[i] @ self.wgu[i][l].t()
+                if self.kernels:
+                    act.append(torch.ops.b200ipc.silu_mul(gu))
+                    continue
                 gate, up = gu.split(self.ffn_local, dim=-1)
                 act.append(F.silu(gate) * up)
             gamma_next = self.norm_attn[l + 1] if l + 1 < cfg.layers else self.norm_final
-            normed, h = self._reduce_norm(h, gamma_next, act, [self.wdown[i][l] for i in range(self.nlocal)])
+            normed, h = self._reduce_norm(h, gamma_next, act, [self.wdown_run[i][l] for i in range(self.nlocal)])
         self.last_hidden = normed  # final-norm output of every local rank (replicated values)
         # vocabulary-parallel head: local arg-max, then the global one over ranks
         best_val, best_idx = [], []

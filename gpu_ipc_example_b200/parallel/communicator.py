@@ -213,17 +213,37 @@ class Communicator:
         self.last_info = CollInfo.from_vec(v)
         return self._ret(x, outs)
 
+    @staticmethod
+    def pack_weight(weight: torch.Tensor) -> torch.Tensor:
+        """Re-lays a row-parallel weight [N, K] (nn.Linear layout, N a multiple of 64) for `linear_allreduce`:
+        [N / 64, K blocks, 64, 64], every 64 x 64 block stored as the 128-byte-swizzled shared-memory image the
+        tensor core reads (16-byte chunk c of row r sits at chunk c ^ (r % 8)), K zero-padded to a multiple of
+        256.  Done once at load time; the kernel then streams the weight with one contiguous bulk copy per
+        stage, which is worth most at decode sizes where the layer is bound by reading the weight."""
+        N, K = weight.shape
+        if N % 64:
+            raise ValueError("pack_weight needs N to be a multiple of 64")
+        kb = (K + 255) // 256 * 4
+        wp = torch.zeros(N, kb * 64, dtype=weight.dtype, device=weight.device)
+        wp[:, :K] = weight
+        blocks = wp.view(N // 64, 64, kb, 8, 8).permute(0, 2, 1, 3, 4)  # [row block, k block, row, chunk, element]
+        r = torch.arange(64, device=weight.device) % 8
+        c = torch.arange(8, device=weight.device)
+        src_chunk = (c[None, :] ^ r[:, None])[None, None, :, :, None].expand(N // 64, kb, 64, 8, 8)
+        return torch.gather(blocks, 3, src_chunk).contiguous().view(N // 64, kb, 64, 64)
+
     def linear_allreduce(self, x: TensorOrList, weight: TensorOrList, residual: Optional[TensorOrList] = None,
                          gamma: Optional[TensorOrList] = None, eps: float = 1e-5, *, ctas: int = 0):
         """Row-parallel linear layer fused with its all-reduce in one tcgen05/TMA kernel.
 
-        x: [M, K_local], weight: [N, K_local] (nn.Linear layout) of this rank.  Returns
+        x: [M, K_local], weight: [N, K_local] (nn.Linear layout) of this rank, or that weight packed once by
+        `pack_weight` (faster, most of all at decode sizes).  Returns
         `y = all_reduce(x @ weight.T)` when neither residual nor gamma is given, else the pair
         `(RMSNorm(y + residual) * gamma, y + residual)`.  Outputs live in the symmetric heap and are
         reused by the next call with the same shape: consume (or copy) them before calling again."""
         xs = [t.contiguous() for t in self._lists(x)]
         ws = [t.contiguous() for t in self._lists(weight)]
-        M, N = xs[0].shape[0], ws[0].shape[0]
+        M, N = xs[0].shape[0], ws[0].shape[0] * (64 if ws[0].dim() == 4 else 1)  # 4-D: packed by pack_weight
         key = (M, N, xs[0].dtype)
         cache = self.__dict__.setdefault("_gemm_buffers", {})
         if key not in cache:
@@ -336,6 +356,30 @@ class Communicator:
     @property
     def seq(self) -> int:
         return self._C.seq(self._h)
+
+    # ------------------------------------------------------------------ device-side trace
+    def set_trace(self, on: bool = True):
+        """Every completed device-side wait of the flag-in-data kernels leaves a time-stamped record (wire, site,
+        peer, step, flag) in a ring inside the rank's heap; `B200IPC_DEBUG=1` in the environment switches it on
+        at creation.  The analogue of the reference's verbose build (allreduce.hpp:96-101)."""
+        self._C.set_trace_wires(self._h, on)
+
+    def trace_events(self, local: int = 0):
+        """The records of the trace ring, oldest first: dicts with t_ns, wire, site, peer, step, flag, rank, and
+        the total number of records written so far (the ring keeps the most recent ones)."""
+        off, entries, rec = self._C.trace_ring(self._h)
+        raw = self.dump_heap(off, 16 + entries * rec, local)
+        total = int(raw[:4].view(torch.int32)[0]) & 0xFFFFFFFF
+        body = raw[16:].view(torch.int64).view(entries, rec // 8)
+        n = min(total, entries)
+        first = total % entries if total > entries else 0
+        out = []
+        for k in range(n):
+            row = body[(first + k) % entries]
+            words = row[1:].contiguous().view(torch.int32).tolist()
+            out.append(dict(t_ns=int(row[0]), wire=words[0], site=words[1], peer=words[2], step=words[3],
+                            flag=words[4] & 0xFFFFFFFF, rank=words[5]))
+        return out, total
 
     def heap_layout(self):
         keys = ("ctrl_off", "scatter_off", "gather_off", "half_bytes", "oneshot_off", "oneshot_bytes", "staging_off",

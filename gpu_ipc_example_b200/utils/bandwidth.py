@@ -50,8 +50,9 @@ def load_peaks(repo_root: str | None = None) -> Peaks:
         return Peaks(1590.0, 1400.0, 6650.0, "fallback")
 
 
-def fused_layer_roofline_seconds(M: int, K: int, N: int, world: int, peaks: Peaks, link_gbs: float = NVLINK_PEER_COPY_GBS) -> float:
-    """Slower of the GEMM at the measured tensor peak and the all-reduce bytes over NVLink."""
+def fused_layer_roofline_seconds(M: int, K: int, N: int, world: int, peaks: Peaks, link_gbs: float = NVLINK_NOMINAL_GBS) -> float:
+    """Slower of the GEMM at the measured tensor peak and the all-reduce bytes over NVLink (by default at the
+    nominal 900 GB/s per direction; pass NVLINK_PEER_COPY_GBS for the measured peer-copy rate)."""
     flops = 2.0 * M * K * N
     link_bytes = 2.0 * (world - 1) / world * M * N * 2 if world > 1 else 0.0
     return max(flops / (peaks.bf16_tflops * 1e12), link_bytes / (link_gbs * 1e9))

@@ -49,9 +49,11 @@ def test_bandwidth_conventions():
     assert utils.allreduce_link_bound_gbs(8, nvls=True) == pytest.approx(770.0 * 14 / 9)
     p = utils.load_peaks("/nonexistent")
     assert p.source == "fallback" and p.bf16_tflops == 1590.0
-    # M = 2048 at TP = 8 is link bound, M = 1 is (nominally) compute bound at a sliver of a microsecond
+    # M = 2048 at TP = 8: at the nominal 900 GB/s the GEMM at the measured peak is the slower side, at the
+    # measured 770 GB/s peer-copy rate the link is; M = 1 is (nominally) compute bound at a sliver of a microsecond
     big = utils.fused_layer_roofline_seconds(2048, 3584, 8192, 8, p)
-    assert big == pytest.approx(2 * 7 / 8 * 2048 * 8192 * 2 / 770e9)
+    assert big == pytest.approx(max(2 * 7 / 8 * 2048 * 8192 * 2 / 900e9, 2 * 2048 * 3584 * 8192 / 1590e12))
+    assert utils.fused_layer_roofline_seconds(2048, 3584, 8192, 8, p, utils.NVLINK_PEER_COPY_GBS) == pytest.approx(2 * 7 / 8 * 2048 * 8192 * 2 / 770e9)
     assert utils.fused_layer_roofline_seconds(1, 3584, 8192, 1, p) == pytest.approx(2 * 3584 * 8192 / 1590e12)
 
 
