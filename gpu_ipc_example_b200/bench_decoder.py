@@ -33,6 +33,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=80)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--no-kernels", action="store_true", help="plain PyTorch ops for RoPE / cache append / attention / SiLU*up")
+    ap.add_argument("--pack", action="store_true", help="gemm arm: row-parallel weights packed by Communicator.pack_weight")
+    ap.add_argument("--breakdown", action="store_true", help="also time the stages of one eager step with CUDA events")
     ap.add_argument("--per-rank-shapes-of", type=int, default=0,
                     help="single-GPU dry run: use the per-rank shapes of this tensor-parallel degree with a world of one")
     args = ap.parse_args()
@@ -68,9 +71,10 @@ def main():
         comm = None
         if multi:
             comm = Communicator.from_torch_distributed(local, staging_bytes=256 << 20, device_seq=True)
-        elif arm == "gemm":
+        elif arm in ("gemm", "allreduce"):
             comm = Communicator.virtual(1, local, staging_bytes=256 << 20, device_seq=True)
-        model = LlamaTP(cfg, comm, batch=args.batch, max_ctx=args.ctx, fusion=arm, seed=3)
+        model = LlamaTP(cfg, comm, batch=args.batch, max_ctx=args.ctx, fusion=arm, seed=3,
+                        kernels=False if args.no_kernels else None, pack_weights=args.pack)
         model.pos = args.ctx - 1  # attend over a full context (the cache holds zeros: timing only)
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
@@ -99,6 +103,18 @@ def main():
         if comm is not None:
             comm.check()
         step = float(t.item())
+        stages = None
+        if args.breakdown:
+            model.pos = args.ctx - 1
+            model.stage_events = []
+            with torch.cuda.stream(stream):
+                model.decode(tokens)
+                stream.synchronize()
+            acc = {}
+            for name, a, b in model.stage_events:
+                acc[name] = acc.get(name, 0.0) + a.elapsed_time(b)
+            stages = {k: round(v, 3) for k, v in acc.items()}  # ms per step, eager launches (host gaps included)
+            model.stage_events = None
         kv_bytes = 2 * args.batch * model.hkv * args.ctx * cfg.head_dim * 2 * cfg.layers
         floor = (model.weight_bytes_per_rank() + kv_bytes) / hbm
         if rank == 0:
@@ -106,7 +122,8 @@ def main():
                 "arm": arm, "world": world, "layers": cfg.layers, "batch": args.batch, "ctx": args.ctx,
                 "ms_per_step": round(step * 1e3, 4), "tokens_per_s": round(args.batch / step, 1),
                 "weight_and_kv_stream_floor_ms": round(floor * 1e3, 4), "fraction_of_floor": round(floor / step, 3),
-                "peaks": peaks, "next_token_sample": int(out[0]),
+                "kernels": bool(model.kernels), "packed_weights": bool(args.pack and arm == "gemm"),
+                "stage_ms_eager": stages, "peaks": peaks, "next_token_sample": int(out[0]),
             }), flush=True)
         del model, graph
         if comm is not None:

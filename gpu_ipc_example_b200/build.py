@@ -28,7 +28,7 @@ CSRC = PKG / "csrc"
 BUILD = PKG / "build"
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 
-LL_OPS = ["ArParallel", "ArSequential", "ArRing", "ArBisect", "ArOneShot", "AgRing", "AgDirect"]
+LL_OPS = ["ArParallel", "ArSequential", "ArRing", "ArBisect", "ArOneShot", "AgRing", "AgDirect", "RsParallel"]
 LL_TYPES = {"f16": "__half", "bf16": "__nv_bfloat16"}
 
 ARCH = "-gencode arch=compute_100a,code=sm_100a"
@@ -164,6 +164,56 @@ def build(with_torch: bool = True, verbose: bool = False, jobs: int | None = Non
         print(proc.stdout)
 
 
+def cuda_units():
+    """(source, extra flags) of every CUDA translation unit of the library."""
+    units = [("coll/ll_inst.cu", f"-DB200_LL_OP={op} -DB200_LL_T={ty}") for op in LL_OPS for ty in LL_TYPES.values()]
+    units += [(src, "") for src in ("coll/bulk_inst.cu", "fused/fused_ops.cu", "fused/gemm_ar.cu", "model/decode_ops.cu",
+                                    "capi/no_alloc.cu")]
+    return units
+
+
+def ptxas_table() -> str:
+    """Compiles every CUDA unit with `-Xptxas -v` (no GPU needed) and returns a markdown table of what the
+    compiler reports per kernel: registers, stack frame, spill stores / loads, static shared memory."""
+    import re
+
+    rows = []
+    for src, extra in cuda_units():
+        cmd = (f"{CUDA_HOME}/bin/nvcc {ARCH} -lineinfo -O3 -std=c++17 --expt-relaxed-constexpr -Xptxas -v {extra} "
+               f"-c {CSRC / src} -o /dev/null")
+        proc = subprocess.run(cmd, shell=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(proc.stdout[-4000:])
+        text = subprocess.run(["c++filt"], input=proc.stdout, stdout=subprocess.PIPE, text=True).stdout
+        name, frame = None, ("0", "0", "0")
+        for line in text.splitlines():
+            m = re.search(r"Compiling entry function '(.*)' for", line)
+            if m:
+                name = m.group(1)
+                continue
+            m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if m:
+                frame = m.groups()
+                continue
+            m = re.search(r"Used (\d+) registers(?:, used \d+ barriers)?(?:, (\d+) bytes smem)?", line)
+            if m and name:
+                short = name.replace("void ", "").replace("b200ipc::", "").replace("(anonymous namespace)::", "")
+                depth = 0  # drop the trailing parameter list
+                for i in range(len(short) - 1, -1, -1):
+                    depth += (short[i] == ")") - (short[i] == "(")
+                    if depth == 0:
+                        short = short[:i]
+                        break
+                rows.append((short, m.group(1), frame[0], frame[1], frame[2], m.group(2) or "0"))
+                name = None
+    out = ["| kernel | registers | stack B | spill st B | spill ld B | static smem B |", "|---|---|---|---|---|---|"]
+    out += ["| `" + r[0] + "` | " + " | ".join(r[1:]) + " |" for r in rows]
+    return "\n".join(out) + "\n"
+
+
 if __name__ == "__main__":
+    if "--ptxas-table" in sys.argv:
+        print(ptxas_table())
+        sys.exit(0)
     build(with_torch="--no-torch" not in sys.argv, verbose="-v" in sys.argv)
     print("built:", ", ".join(sorted(p.name for p in PKG.glob("*.so"))))

@@ -112,7 +112,9 @@ void usage() {
       "      --no-rotate     reuse one buffer (default: rotate over buffers that together exceed L2)\n"
       "      --json FILE     append one JSON object per (algorithm, size) row\n"
       "      --csv FILE      append one CSV line per row\n"
-      "  -a also takes a comma separated list; `nccl` and `nccl_allgather` in it time NCCL\n",
+      "  -a also takes a comma separated list; `nccl`, `nccl_allgather` and `nccl_reduce_scatter` in it\n"
+      "  time NCCL; `reduce_scatter` (auto) and `reduce_scatter:<parallel:ll512|bulk|nvls|...>` time the\n"
+      "  reduce-scatter (-n then counts the whole input)\n",
       algo_names_help().c_str());
 }
 
@@ -192,6 +194,7 @@ struct AlgoEntry {
   std::string name;
   AlgoSpec spec;
   bool is_ag = false;
+  bool is_rs = false;  // reduce-scatter: `elements` counts the whole input, every rank keeps 1/world of the sum
   bool nccl = false;
 };
 
@@ -216,17 +219,27 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
 
   // ---- which algorithms ------------------------------------------------------------------
   std::vector<AlgoEntry> algos;
-  bool any_nccl = false, any_ag = false, any_ar = false;
+  bool any_nccl = false, any_ag = false, any_ar = false, any_rs = false;
   for (const std::string& name : split_commas(opt.algo)) {
     AlgoEntry e;
     e.name = name;
-    if (name == "nccl" || name == "nccl_allgather") {
+    if (name == "nccl" || name == "nccl_allgather" || name == "nccl_reduce_scatter") {
       e.nccl = true;
       e.is_ag = name == "nccl_allgather";
+      e.is_rs = name == "nccl_reduce_scatter";
+    } else if (name.rfind("reduce_scatter", 0) == 0) {
+      // "reduce_scatter" (auto) or "reduce_scatter:<parallel:ll512|simple_pcie_p|bulk|nvls|...>"
+      e.is_rs = true;
+      bool ag = false;
+      const std::string rest = name.size() > 15 ? name.substr(15) : std::string("auto");
+      if (!parse_algo(rest, &e.spec, &ag) || ag) {
+        std::fprintf(stderr, "unknown reduce-scatter algorithm '%s'\n", name.c_str());
+        return 2;
+      }
     } else if (!parse_algo(name, &e.spec, &e.is_ag)) {
       // with --baseline nccl the -a value only says which collective: anything naming "allgather" is one
       if (opt.baseline != "nccl") {
-        std::fprintf(stderr, "unknown algorithm '%s'\nknown: %s nccl nccl_allgather\n", name.c_str(), algo_names_help().c_str());
+        std::fprintf(stderr, "unknown algorithm '%s'\nknown: %s reduce_scatter[:<algo>] nccl nccl_allgather nccl_reduce_scatter\n", name.c_str(), algo_names_help().c_str());
         return 2;
       }
       e.is_ag = name.find("allgather") != std::string::npos;
@@ -234,6 +247,7 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
     if (opt.baseline == "nccl") e.nccl = true;
     any_nccl |= e.nccl;
     (e.is_ag ? any_ag : any_ar) = true;
+    any_rs |= e.is_rs;
     algos.push_back(e);
   }
   B200_REQUIRE(!algos.empty(), "no algorithm given");
@@ -260,7 +274,7 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
   // ---- buffer pools: a rotating set per size, carved out of one pool ----------------------------
   auto in_bytes = [&](size_t n) { return round_up(n * 2, 256); };
   auto out_bytes = [&](size_t n) { return round_up(n * 2 * (any_ag ? size_t(world) : 1), 256); };
-  const bool separate_out = any_ag || opt.out_of_place;
+  const bool separate_out = any_ag || any_rs || opt.out_of_place;
   auto nbuf_for = [&](size_t n) -> int {
     if (opt.verify || opt.no_rotate) return 1;
     const size_t set = in_bytes(n) + (separate_out ? out_bytes(n) : 0);
@@ -366,6 +380,7 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
 
   for (const AlgoEntry& algo : algos) {
     const bool is_ag = algo.is_ag;
+    const bool is_rs = algo.is_rs;
     if (rank == 0 && !opt.verify) {
       std::printf("# algo %s\n", algo.name.c_str());
       std::printf("# %12s %10s %6s %6s %12s %12s %12s %10s %10s\n", "elements", "bytes", "ctas", "warps", "us_min(max)", "us_median",
@@ -373,7 +388,8 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
     }
     for (size_t n : sizes) {
       const int nbuf = nbuf_for(n);
-      const size_t out_n = is_ag ? n * size_t(world) : n;
+      if (is_rs && n % (8 * size_t(world)) != 0) continue;
+      const size_t out_n = is_ag ? n * size_t(world) : (is_rs ? n / size_t(world) : n);
       auto in_ptr = [&](int i, int k) { return static_cast<void*>(in_pool[size_t(i)] + size_t(k) * in_bytes(n)); };
       auto out_ptr = [&](int i, int k) {
         return separate_out ? static_cast<void*>(out_pool[size_t(i)] + size_t(k) * out_bytes(n)) : in_ptr(i, k);
@@ -415,10 +431,12 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
         LaunchGeom g{opt.groups, opt.subgroups};
         if (algo.nccl) {
           if (is_ag) nccl->all_gather(ins[0], outs[0], n, dt == DType::F16 ? 0 : 1, stream);
+          else if (is_rs) nccl->reduce_scatter(ins[0], outs[0], n / size_t(world), dt == DType::F16 ? 0 : 1, stream);
           else nccl->all_reduce(ins[0], outs[0], n, dt == DType::F16 ? 0 : 1, stream);
           return CollInfo{};
         }
         if (is_ag) return comm->all_gather(algo.spec, dt, ins.data(), outs.data(), n, g, stream, flags);
+        if (is_rs) return comm->reduce_scatter(algo.spec, dt, ins.data(), outs.data(), n, g, stream, flags);
         return comm->all_reduce(algo.spec, dt, ins.data(), outs.data(), n, g, stream, flags);
       };
 
@@ -432,14 +450,15 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
         // expected result on the CPU, from regenerated inputs of every rank
         std::vector<const uint16_t*> all;
         for (int r = 0; r < world; ++r) all.push_back(host_in[size_t(r)].data());
-        std::vector<uint16_t> want(out_n), got(out_n);
+        std::vector<uint16_t> want(is_rs ? n : out_n), got(out_n);
         if (is_ag) cpu_all_gather(all, want.data(), n);
         else cpu_all_reduce(dt, all, want.data(), n, opt.ref_accum);
         const bool exact = is_ag || (!opt.random && dt == DType::F16);
         size_t bad = 0;
         for (int i = 0; i < nlocal; ++i) {
           B200_CUDA_CHECK(cudaMemcpy(got.data(), out_ptr(i, 0), out_n * 2, cudaMemcpyDeviceToHost));
-          VerifyReport rep = verify_buffer(dt, got.data(), want.data(), out_n, exact, dt == DType::F16 ? 2e-2f : 1.5e-1f,
+          const uint16_t* want_i = want.data() + (is_rs ? size_t(comm->rank(i)) * out_n : 0);
+          VerifyReport rep = verify_buffer(dt, got.data(), want_i, out_n, exact, dt == DType::F16 ? 2e-2f : 1.5e-1f,
                                            dt == DType::F16 ? 4e-3f : 3e-2f);
           if (rep.mismatches) {
             std::printf("[%d] Error Compare! %zu of %zu elements differ; first at %zu: expected %g, got %g\n", comm->rank(i),
@@ -477,7 +496,7 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
       std::vector<double> sample_ns;
       double ns_local_last = 0;
       for (int sidx = 0; sidx < opt.samples; ++sidx) {
-        if (!is_ag && !opt.out_of_place) fill_inputs(false);  // in place: every sample starts from fresh data
+        if (!is_ag && !is_rs && !opt.out_of_place) fill_inputs(false);  // in place: every sample starts from fresh data
         comm->host_barrier();
         B200_CUDA_CHECK(cudaEventRecord(ev0, stream));
         if (exec) {
@@ -506,12 +525,12 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
       if (rank == 0) {
         const double bytes = double(n) * 2;
         const double algbw = (is_ag ? bytes * world : bytes) / ns_med;  // GB/s
-        const double busbw = is_ag ? algbw * (world - 1) / world : algbw * 2 * (world - 1) / world;
+        const double busbw = (is_ag || is_rs) ? algbw * (world - 1) / world : algbw * 2 * (world - 1) / world;
         std::printf("  %12zu %10.0f %6d %6d %12.2f %12.2f %12.2f %10.2f %10.2f\n", n, bytes, info.ctas, info.warps, ns_min / 1e3,
                     ns_med / 1e3, ns_hi / 1e3, algbw, busbw);
         std::fflush(stdout);
-        const char* coll = is_ag ? "all_gather" : "all_reduce";
-        const char* place = is_ag ? "out_of_place" : (opt.out_of_place ? "out_of_place" : "in_place");
+        const char* coll = is_ag ? "all_gather" : (is_rs ? "reduce_scatter" : "all_reduce");
+        const char* place = (is_ag || is_rs) ? "out_of_place" : (opt.out_of_place ? "out_of_place" : "in_place");
         const char* timing = exec ? "graph_replay" : "launch_loop";
         const char* dname = dt == DType::F16 ? "fp16" : "bf16";
         if (json) {

@@ -30,6 +30,7 @@ class NcclBaseline {
     init_rank_ = sym<int (*)(Comm*, int, UniqueId, int)>("ncclCommInitRank");
     all_reduce_ = sym<int (*)(const void*, void*, size_t, int, int, Comm, cudaStream_t)>("ncclAllReduce");
     all_gather_ = sym<int (*)(const void*, void*, size_t, int, Comm, cudaStream_t)>("ncclAllGather");
+    reduce_scatter_ = sym<int (*)(const void*, void*, size_t, int, int, Comm, cudaStream_t)>("ncclReduceScatter");
     destroy_ = sym<int (*)(Comm)>("ncclCommDestroy");
     get_version_ = sym<int (*)(int*)>("ncclGetVersion");
     B200_CUDA_CHECK(cudaSetDevice(device));
@@ -56,6 +57,10 @@ class NcclBaseline {
   void all_gather(const void* in, void* out, size_t n, int dtype, cudaStream_t s) {
     check(all_gather_(in, out, n, dtype == 0 ? 6 : 9, comm_, s), "ncclAllGather");
   }
+  // n: elements every rank receives
+  void reduce_scatter(const void* in, void* out, size_t n, int dtype, cudaStream_t s) {
+    check(reduce_scatter_(in, out, n, dtype == 0 ? 6 : 9, 0 /* sum */, comm_, s), "ncclReduceScatter");
+  }
 
  private:
   template <typename F>
@@ -72,6 +77,7 @@ class NcclBaseline {
   int (*init_rank_)(Comm*, int, UniqueId, int) = nullptr;
   int (*all_reduce_)(const void*, void*, size_t, int, int, Comm, cudaStream_t) = nullptr;
   int (*all_gather_)(const void*, void*, size_t, int, Comm, cudaStream_t) = nullptr;
+  int (*reduce_scatter_)(const void*, void*, size_t, int, int, Comm, cudaStream_t) = nullptr;
   int (*destroy_)(Comm) = nullptr;
   int (*get_version_)(int*) = nullptr;
 };

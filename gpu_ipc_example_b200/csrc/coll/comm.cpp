@@ -409,6 +409,13 @@ CollInfo Comm::launch_ll(LLOpId op, AlgoSpec algo, DType t, const void* const* i
       B200_REQUIRE(nelems % 2 == 0, "all-gather needs an even element count per rank (shards start on a dword)");
       need = cdiv(int64_t(nelems / 2), payload);
       break;
+    case LLOpId::RsParallel:
+      B200_REQUIRE(nelems % (2 * size_t(N)) == 0,
+                   "flag-in-data reduce-scatter needs a multiple of 2 x world elements (slices start on a dword)");
+      unit = N;
+      need = cdiv(int64_t(nelems / size_t(N) / 2), payload) * N;
+      slots = kParallelSlots;
+      break;
   }
   if (need < unit) need = unit;
 
@@ -447,6 +454,12 @@ CollInfo Comm::launch_ll(LLOpId op, AlgoSpec algo, DType t, const void* const* i
     case LLOpId::ArSequential:
     case LLOpId::ArRing: p.steps = sequential_steps(nelems, N, p.nwires, payload); break;
     case LLOpId::ArOneShot: p.steps = oneshot_steps(nelems, p.nwires, payload); break;
+    case LLOpId::RsParallel:
+      p.steps = reduce_scatter_steps(nelems, N, p.nwires, payload);
+      B200_REQUIRE(p.steps <= kParallelSlots, "flag-in-data reduce-scatter: " << nelems << " elements need " << p.steps
+                                                  << " steps on " << p.nwires << " wires, more than the "
+                                                  << kParallelSlots << " a launch may take; use more wires or bulk/nvls");
+      break;
     default: p.steps = allgather_steps(nelems, p.nwires, payload); break;
   }
 
@@ -456,11 +469,15 @@ CollInfo Comm::launch_ll(LLOpId op, AlgoSpec algo, DType t, const void* const* i
     case LLOpId::ArParallel: ring_bytes = size_t(p.nwires) * kParallelSlots * txn; break;
     case LLOpId::ArBisect: ring_bytes = size_t(kBisectFarBase + int64_t(p.nwires) * kParallelSlots) * txn; break;
     case LLOpId::ArOneShot: ring_bytes = 0; break;
+    case LLOpId::RsParallel: ring_bytes = 2 * size_t(p.nwires) * kParallelSlots * txn; break;
     default: ring_bytes = size_t(N) * kSequentialSlots * p.nwires * txn; break;
   }
   B200_REQUIRE(ring_bytes <= lay.half_bytes, "scratch ring too small for this geometry");
 
-  const uint32_t adv = (op == LLOpId::ArOneShot) ? uint32_t(p.steps + 1) : seq_advance(p.steps, slots);
+  // reduce-scatter: always 2, so that bit 1 of the sequence number (the ring half) alternates
+  const uint32_t adv = (op == LLOpId::ArOneShot)    ? uint32_t(p.steps + 1)
+                       : (op == LLOpId::RsParallel) ? 2u
+                                                    : seq_advance(p.steps, slots);
   const uint32_t first = take_seq(adv);
 
   KArgs args;
@@ -600,10 +617,10 @@ AlgoSpec Comm::choose_all_reduce(size_t bytes, bool symmetric) const {
     // thresholds set by the caller override the built-in table
     if (bytes <= oneshot_max_bytes_) {
       a.sched = SchedKind::OneShot;
-      a.proto = ProtoKind::LL512;
+      a.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
     } else if (bytes <= ll_max_bytes_) {
       a.sched = SchedKind::Parallel;
-      a.proto = ProtoKind::LL512;
+      a.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
     } else {
       a.sched = (has_nvls() && world_ >= 8) ? SchedKind::Nvls : SchedKind::Bulk;
       a.proto = ProtoKind::LL512;
@@ -620,6 +637,7 @@ AlgoSpec Comm::choose_all_reduce(size_t bytes, bool symmetric) const {
     }
   }
   if (a.sched == SchedKind::Nvls && !has_nvls()) a.sched = SchedKind::Bulk;
+  if (safe_protos_ && (a.proto == ProtoKind::LL512 || a.proto == ProtoKind::LL128)) a.proto = ProtoKind::LL16;
   return a;
 }
 
@@ -672,7 +690,7 @@ CollInfo Comm::all_gather(AlgoSpec algo, DType t, const void* const* ins, void* 
     // barrier; measured ahead of the barrier-based kernels and of NCCL up to 64 MiB per rank
     if (world_ == 2 || bytes <= (size_t(1) << 20) / size_t(world_) || nelems % 8 != 0) {
       algo.sched = SchedKind::Ring;
-      algo.proto = ProtoKind::LL512;
+      algo.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
       algo.direct_allgather = true;
     } else {
       algo.sched = has_nvls() ? SchedKind::Nvls : SchedKind::Bulk;
@@ -696,8 +714,22 @@ CollInfo Comm::reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, vo
     info.sched = SchedKind::Bulk;
     return info;
   }
-  bool nvls = algo.automatic ? has_nvls() : (algo.sched == SchedKind::Nvls);
-  return launch_bulk(BulkModeId::ReduceScatter, nvls, t, ins, outs, nelems, geom, stream, extra_flags);
+  if (algo.automatic) {
+    algo = AlgoSpec{};
+    // small inputs: one flag-in-data push to each slice's owner, no barrier
+    if (nelems % (2 * size_t(world_)) == 0 && nelems * 2 <= kReduceScatterLLMaxBytes) {
+      algo.sched = SchedKind::Parallel;
+      algo.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
+    } else {
+      algo.sched = has_nvls() ? SchedKind::Nvls : SchedKind::Bulk;
+    }
+  }
+  if (algo.sched == SchedKind::Parallel)
+    return launch_ll(LLOpId::RsParallel, algo, t, ins, outs, nelems, geom, stream, extra_flags);
+  B200_REQUIRE(algo.sched == SchedKind::Bulk || algo.sched == SchedKind::Nvls,
+               "reduce-scatter runs on the parallel (flag-in-data), bulk or nvls schedules");
+  return launch_bulk(BulkModeId::ReduceScatter, algo.sched == SchedKind::Nvls, t, ins, outs, nelems, geom, stream,
+                     extra_flags);
 }
 
 }  // namespace b200ipc

@@ -68,6 +68,10 @@ struct CommOptions {
   int max_ctas = 0;         // cap on CTAs per launch (0 = fill the GPU)
 };
 
+// Largest input (bytes) that `auto` gives to the flag-in-data reduce-scatter: a launch takes at
+// most kParallelSlots steps, and this much fits in them at the default geometry with every proto.
+constexpr size_t kReduceScatterLLMaxBytes = size_t(2) << 20;
+
 class Comm {
  public:
   static std::unique_ptr<Comm> create(UnixMesh& mesh, int device, const CommOptions& opt);
@@ -126,6 +130,10 @@ class Comm {
   bool device_seq() const { return device_seq_; }
   void set_seq(uint32_t s) { seq_ = s; }
   uint64_t launches() const { return launches_; }
+  // After a failed self-test of the 64-byte-segment wire formats (LL128 / LL512 rely on a warp's aligned
+  // 64-byte store arriving whole): `auto` then only uses formats whose atomic unit is an 8-byte granule.
+  void set_safe_protos(bool on) { safe_protos_ = on; }
+  bool safe_protos() const { return safe_protos_; }
   bool trace_wires() const { return trace_wires_; }
   void set_trace_wires(bool on) { trace_wires_ = on; }
   void set_timeout_ms(uint64_t ms) { timeout_ns_ = ms * 1000000ull; }
@@ -190,6 +198,7 @@ class Comm {
   uint32_t ag_arrive_ = 0;
   uint32_t ag_launches_ = 0;
   bool device_seq_ = false;
+  bool safe_protos_ = false;
   bool trace_wires_ = false;  // B200IPC_DEBUG=1: kernels leave a record per completed wait in the trace ring
   uint64_t timeout_ns_ = 2000000000ull;
   int max_ctas_ = 0;

@@ -14,6 +14,7 @@ enum class LLOpId : int {
   ArOneShot = 4,
   AgRing = 5,
   AgDirect = 6,
+  RsParallel = 7,
 };
 enum class BulkModeId : int { AllReduce = 0, ReduceScatter = 1, AllGather = 2 };
 

@@ -41,6 +41,7 @@ enum class LLOp : int {
   ArOneShot,
   AgRing,
   AgDirect,
+  RsParallel,
 };
 
 template <LLOp OP, ProtoKind K, typename T, int N>
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(1024) ll_kernel(const __grid_constant__ KArgs 
   else if constexpr (OP == LLOp::ArBisect) run_bisect<B, N>(c, wire);
   else if constexpr (OP == LLOp::ArOneShot) run_oneshot<B, N>(c, wire);
   else if constexpr (OP == LLOp::AgRing) run_ring_allgather<B, N>(c, wire);
+  else if constexpr (OP == LLOp::RsParallel) run_reduce_scatter<B, N>(c, wire);
   else run_direct_allgather<B, N>(c, wire);
   if (me.seq_dev) {
     // The last CTA to finish advances the offset; every CTA has read it by then.

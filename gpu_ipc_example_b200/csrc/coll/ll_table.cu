@@ -9,7 +9,8 @@
 
 namespace b200ipc {
 
-static_assert(int(LLOpId::ArParallel) == int(LLOp::ArParallel) && int(LLOpId::AgDirect) == int(LLOp::AgDirect),
+static_assert(int(LLOpId::ArParallel) == int(LLOp::ArParallel) && int(LLOpId::AgDirect) == int(LLOp::AgDirect) &&
+                  int(LLOpId::RsParallel) == int(LLOp::RsParallel),
               "LLOpId must mirror LLOp");
 static_assert(kBulkThreadsPerCta == kBulkThreads, "thread count mismatch");
 static_assert(kBulkCopyInBit == kBulkCopyIn && kBulkCopyOutBit == kBulkCopyOut, "flag mismatch");
@@ -24,6 +25,7 @@ B200_DECLARE(ArBisect)
 B200_DECLARE(ArOneShot)
 B200_DECLARE(AgRing)
 B200_DECLARE(AgDirect)
+B200_DECLARE(RsParallel)
 #undef B200_DECLARE
 
 template <typename T>
@@ -35,6 +37,7 @@ static KernelFn by_op(LLOpId op, ProtoKind k, int world) {
     case LLOpId::ArBisect: return ll_lookup<LLOp::ArBisect, T>(k, world);
     case LLOpId::ArOneShot: return ll_lookup<LLOp::ArOneShot, T>(k, world);
     case LLOpId::AgRing: return ll_lookup<LLOp::AgRing, T>(k, world);
+    case LLOpId::RsParallel: return ll_lookup<LLOp::RsParallel, T>(k, world);
     default: return ll_lookup<LLOp::AgDirect, T>(k, world);
   }
 }

@@ -230,6 +230,57 @@ B200_HD void run_parallel(const Ctx<B>& c, int wire) {
 }
 
 // ---------------------------------------------------------------------------
+// Reduce-scatter: the first phase of the parallel schedule on its own.  nelems
+// counts the whole input (a multiple of 8 * world elements); rank r's output is
+// the r-th of `world` equal slices, reduced.  A sender gets no reply here, so two
+// things replace the request/response coupling of the all-reduce: a launch never
+// takes more steps than a ring has slots (the host sees to it), and consecutive
+// launches use different halves of the ring (picked by bit 1 of the sequence
+// number, which advances by 2 per launch) - a rank cannot be more than one
+// launch ahead of a peer, because as an owner it needs every peer's slices of
+// the current launch to finish it.
+// ---------------------------------------------------------------------------
+B200_HD int64_t reduce_scatter_steps(uint64_t nelems, int world, int nwires, int payload_dw) {
+  return ceil_div64(int64_t(nelems / uint64_t(world) / 2), int64_t(nwires / world) * payload_dw);
+}
+
+template <class B, int N>
+B200_HD void run_reduce_scatter(const Ctx<B>& c, int wire) {
+  const int r = c.rank;
+  const int ngroups = c.nwires / N;
+  const int g = wire / N;
+  const int y = wire % N;
+  if (g >= ngroups) return;
+  const int64_t chunk_dw = int64_t(c.nelems / uint64_t(N) / 2);
+  const int64_t steps = ceil_div64(chunk_dw, int64_t(ngroups) * B::kPayloadDw);
+  const int64_t ring0 = int64_t((c.seq >> 1) & 1u) * c.nwires * kParallelSlots;  // this launch's half, in transactions
+  const uint32_t flag = c.seq;
+  for (int64_t t = 0; t < steps; ++t) {
+    const int slot = int(t);
+    const int64_t dw = (t * ngroups + g) * B::kPayloadDw;  // inside the chunk
+    typename B::Msg v;
+    B::load(v, c.in, int64_t(y) * chunk_dw + dw, int64_t(y + 1) * chunk_dw, -1);
+    B::shuffle(v);
+    if (y != r) {
+      B::set_flags(v, flag);
+      c.send(txn_at<B>(c.peer_sink(0, y), ring0 + (int64_t(g) * N + r) * kParallelSlots + slot), v);
+    } else {
+      typename B::Acc a;
+      B::acc_init(a, v);
+      if (!recv_in_order<B, 1, N>(
+              c, flag, 0, t, -1, v,
+              [&](int i) -> const char* { return txn_at<B>(c.sink(0), ring0 + (int64_t(g) * N + (r + i) % N) * kParallelSlots + slot); },
+              [&](int i) { return (r + i) % N; },
+              [&](int, const typename B::Msg& x) { B::acc_add(a, x, c.round_each()); }))
+        return;
+      B::acc_to_msg(v, a);
+      B::restore(v);
+      B::store(c.out, dw, chunk_dw, -1, v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Sequential all-reduce: one wire does the whole exchange for its offset, for
 // all peers.  Needs no progress guarantee between warps of a rank.
 // ---------------------------------------------------------------------------

@@ -32,7 +32,7 @@ namespace b200ipc {
 namespace {
 
 struct EmuJob {
-  int op;      // LLOpId numbering: 0 parallel, 1 sequential, 2 ring, 3 bisect, 4 oneshot, 5 ag ring, 6 ag direct
+  int op;      // LLOpId numbering: 0 parallel, 1 sequential, 2 ring, 3 bisect, 4 oneshot, 5 ag ring, 6 ag direct, 7 reduce-scatter
   int proto;   // ProtoKind
   int dtype;   // DType
   int world;
@@ -72,6 +72,7 @@ void run_rank_typed(const EmuJob& job, const RankView& view, const HeapLayout& l
       case 3: run_bisect<B, N>(c, w); break;
       case 4: run_oneshot<B, N>(c, w); break;
       case 5: run_ring_allgather<B, N>(c, w); break;
+      case 7: run_reduce_scatter<B, N>(c, w); break;
       default: run_direct_allgather<B, N>(c, w); break;
     }
   }
@@ -110,6 +111,10 @@ bool geometry_ok(const EmuJob& job) {
   if (job.op == 4) return job.nwires <= kMaxOneShotWires;
   if (job.nwires > kMaxWires) return false;
   if (job.op == 0) return job.nwires % job.world == 0;
+  if (job.op == 7)
+    return job.nwires % job.world == 0 && job.nelems % (2 * uint64_t(job.world)) == 0 &&
+           reduce_scatter_steps(job.nelems, job.world, job.nwires, payload_dw_of(static_cast<ProtoKind>(job.proto))) <=
+               kParallelSlots;
   if (job.op == 3) return job.world % 2 == 0 && job.nwires % (job.world / 2) == 0;
   if (job.op >= 5) return job.nelems % 2 == 0;
   return true;
@@ -134,6 +139,7 @@ uint32_t b200emu_seq_advance(int op, int proto, int world, int nwires, uint64_t 
     case 2: return seq_advance(sequential_steps(nelems, world, nwires, payload), kSequentialSlots);
     case 3: return seq_advance(bisect_steps(nelems, world, nwires, payload), kParallelSlots);
     case 4: return uint32_t(oneshot_steps(nelems, nwires, payload) + 1);
+    case 7: return 2;
     default: return seq_advance(allgather_steps(nelems, nwires, payload), kSequentialSlots);
   }
 }

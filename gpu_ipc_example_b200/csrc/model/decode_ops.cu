@@ -279,6 +279,76 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// res_out = x + residual ; out = RMSNorm(res_out) * gamma.  One CTA per row, one pass: the row's sum stays in
+// registers between the statistic and the scaling (rows of up to 8 x 4 x 256 elements, else a second read).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                                                           const T* __restrict__ gamma, T* __restrict__ out, T* __restrict__ res_out,
+                                                           int hidden, float eps) {
+  using T2 = typename Num<T>::T2;
+  constexpr int U = 4;
+  const int64_t row = blockIdx.x;
+  const int nvec = hidden / 8;
+  const T* xr = x + row * hidden;
+  const T* rr = residual + row * hidden;
+  T* orow = out + row * hidden;
+  T* srow = res_out + row * hidden;
+  __shared__ float s_part[8];
+  uint4 keep[U];
+  float ss = 0.f;
+  const bool in_regs = nvec <= U * int(blockDim.x);
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += U * blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * blockDim.x;
+      if (v >= nvec) continue;
+      const uint4 a = *reinterpret_cast<const uint4*>(xr + size_t(v) * 8);
+      const uint4 b = *reinterpret_cast<const uint4*>(rr + size_t(v) * 8);
+      const T2* pa = reinterpret_cast<const T2*>(&a);
+      const T2* pb = reinterpret_cast<const T2*>(&b);
+      uint4 o;
+      T2* po = reinterpret_cast<T2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = Num<T>::up(pa[e]), fb = Num<T>::up(pb[e]);
+        po[e] = Num<T>::down(fa.x + fb.x, fa.y + fb.y);
+        const float2 r = Num<T>::up(po[e]);
+        ss += r.x * r.x + r.y * r.y;
+      }
+      *reinterpret_cast<uint4*>(srow + size_t(v) * 8) = o;
+      if (in_regs) keep[u] = o;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < int(blockDim.x >> 5); ++w) tot += s_part[w];
+  const float inv = rsqrtf(tot / float(hidden) + eps);
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += U * blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * blockDim.x;
+      if (v >= nvec) continue;
+      const uint4 xv = in_regs ? keep[u] : *reinterpret_cast<const uint4*>(srow + size_t(v) * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(gamma + size_t(v) * 8);
+      const T2* px = reinterpret_cast<const T2*>(&xv);
+      const T2* pg = reinterpret_cast<const T2*>(&g);
+      uint4 o;
+      T2* po = reinterpret_cast<T2*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fx = Num<T>::up(px[e]), fg = Num<T>::up(pg[e]);
+        po[e] = Num<T>::down(fx.x * inv * fg.x, fx.y * inv * fg.y);
+      }
+      *reinterpret_cast<uint4*>(orow + size_t(v) * 8) = o;
+    }
+  }
+}
+
 template <typename T>
 void launch_attention(int G, dim3 grid, cudaStream_t stream, const T* q, const T* k, const T* v, T* out, float* part,
                       unsigned int* counters, int hq, int hkv, int max_ctx, int ctx, int q_row_stride, float scale_log2) {
@@ -344,6 +414,20 @@ void decode_attention(DType t, const void* q, int q_row_stride, const void* kcac
     launch_attention<__nv_bfloat16>(G, grid, stream, static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kcache),
                                     static_cast<const __nv_bfloat16*>(vcache), static_cast<__nv_bfloat16*>(out), part, counters, hq, hkv,
                                     max_ctx, ctx, q_row_stride, scale_log2);
+  B200_CUDA_CHECK(cudaGetLastError());
+}
+
+void add_rmsnorm(DType t, const void* x, const void* residual, const void* gamma, void* out, void* res_out, int64_t rows, int hidden,
+                 float eps, cudaStream_t stream) {
+  B200_REQUIRE(hidden % 8 == 0 && rows > 0, "add_rmsnorm: hidden must be a multiple of 8");
+  if (t == DType::F16)
+    add_rmsnorm_kernel<__half><<<unsigned(rows), 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(residual),
+                                                                  static_cast<const __half*>(gamma), static_cast<__half*>(out),
+                                                                  static_cast<__half*>(res_out), hidden, eps);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<unsigned(rows), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(gamma),
+        static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(res_out), hidden, eps);
   B200_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -27,6 +27,11 @@ size_t decode_attention_workspace_bytes(int batch, int hq, int hkv, int splits);
 void decode_attention(DType t, const void* q, int q_row_stride, const void* kcache, const void* vcache, void* out, void* workspace,
                       int batch, int hq, int hkv, int head_dim, int max_ctx, int ctx, int splits, cudaStream_t stream);
 
+// res_out = x + residual ; out = RMSNorm(res_out) * gamma, row by row ([rows, hidden], 16-byte aligned).  The local
+// half of "all-reduce, then residual add and RMSNorm" when the all-reduce is too large for the one-shot fused kernel.
+void add_rmsnorm(DType t, const void* x, const void* residual, const void* gamma, void* out, void* res_out, int64_t rows, int hidden,
+                 float eps, cudaStream_t stream);
+
 // act[rows, ffn] = silu(gate_up[:, :ffn]) * gate_up[:, ffn:]
 void silu_mul(DType t, const void* gate_up, void* act, int64_t rows, int ffn, int sm_count, cudaStream_t stream);
 

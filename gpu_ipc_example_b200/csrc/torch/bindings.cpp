@@ -381,6 +381,18 @@ at::Tensor decode_attention_op(at::Tensor qkv, at::Tensor kcache, at::Tensor vca
   return out;
 }
 
+// (RMSNorm(x + residual) * gamma, x + residual) for [rows, hidden] tensors
+std::vector<at::Tensor> add_rmsnorm_op(at::Tensor x, at::Tensor residual, at::Tensor gamma, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && residual.is_contiguous() && gamma.is_contiguous() && x.dim() == 2 &&
+                  residual.sizes() == x.sizes() && gamma.numel() == x.size(1) && x.size(1) % 8 == 0,
+              "b200ipc: add_rmsnorm takes contiguous [rows, hidden] tensors, hidden a multiple of 8");
+  at::Tensor out = at::empty_like(x), res_out = at::empty_like(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  add_rmsnorm(dtype_of(x), x.data_ptr(), residual.data_ptr(), gamma.data_ptr(), out.data_ptr(), res_out.data_ptr(), x.size(0),
+              int(x.size(1)), float(eps), at::cuda::getCurrentCUDAStream(x.get_device()));
+  return {out, res_out};
+}
+
 // [rows, 2 F] -> [rows, F]: silu(first half) * second half
 at::Tensor silu_mul_op(at::Tensor gate_up) {
   TORCH_CHECK(gate_up.is_cuda() && gate_up.is_contiguous() && gate_up.dim() == 2 && gate_up.size(1) % 16 == 0,
@@ -416,6 +428,7 @@ TORCH_LIBRARY(b200ipc, m) {
   m.def("decode_attention(Tensor qkv, Tensor kcache, Tensor vcache, Tensor(a!) workspace, int hq, int hkv, int ctx, int splits) -> Tensor",
         &decode_attention_op);
   m.def("silu_mul(Tensor gate_up) -> Tensor", &silu_mul_op);
+  m.def("add_rmsnorm(Tensor x, Tensor residual, Tensor gamma, float eps) -> Tensor[]", &add_rmsnorm_op);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -448,6 +461,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     get(id).heap(int(local)).dump(size_t(offset), size_t(bytes), t.data_ptr());
     return t;
   });
+  m.def("set_safe_protos", [](int64_t id, bool on) { get(id).set_safe_protos(on); });
+  m.def("safe_protos", [](int64_t id) { return get(id).safe_protos(); });
   m.def("set_trace_wires", [](int64_t id, bool on) { get(id).set_trace_wires(on); });
   m.def("trace_wires", [](int64_t id) { return get(id).trace_wires(); });
   // (offset of the trace ring inside the heap, number of records it holds, bytes per record)

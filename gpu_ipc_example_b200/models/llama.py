@@ -114,6 +114,7 @@ class LlamaTP:
             self.kcache.append([torch.zeros(batch, self.hkv, max_ctx, D, device=dev, dtype=dt) for _ in range(cfg.layers)])
             self.vcache.append([torch.zeros(batch, self.hkv, max_ctx, D, device=dev, dtype=dt) for _ in range(cfg.layers)])
         self.pos = 0
+        self.stage_events = None  # a list: decode() then appends (stage name, start event, end event)
         if self.kernels:
             from .._ext import load
 
@@ -159,6 +160,23 @@ class LlamaTP:
         s = parts[0] + residual[0]
         return [rms_norm(s, gamma, eps)], [s]
 
+    def _stage(self, name):
+        """Context manager that brackets a stage of the step with CUDA events when `stage_events` is a list."""
+        import contextlib
+
+        if self.stage_events is None:
+            return contextlib.nullcontext()
+
+        @contextlib.contextmanager
+        def cm():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            yield
+            b.record()
+            self.stage_events.append((name, a, b))
+
+        return cm()
+
     # ------------------------------------------------------------------ one decode step
     @torch.no_grad()
     def decode(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -172,11 +190,14 @@ class LlamaTP:
         for l in range(cfg.layers):
             attn_out = []
             for i in range(self.nlocal):
-                qkv = normed[i] @ self.wqkv[i][l].t()
+                with self._stage("qkv_gemm"):
+                    qkv = normed[i] @ self.wqkv[i][l].t()
                 if self.kernels:
-                    torch.ops.b200ipc.rope_kv_append(qkv, self.kcache[i][l], self.vcache[i][l], self.hq, self.hkv, pos, cfg.rope_theta)
-                    attn_out.append(torch.ops.b200ipc.decode_attention(qkv, self.kcache[i][l], self.vcache[i][l], self.attn_ws[i],
-                                                                       self.hq, self.hkv, pos + 1, self.attn_splits))
+                    with self._stage("rope_append"):
+                        torch.ops.b200ipc.rope_kv_append(qkv, self.kcache[i][l], self.vcache[i][l], self.hq, self.hkv, pos, cfg.rope_theta)
+                    with self._stage("attention"):
+                        attn_out.append(torch.ops.b200ipc.decode_attention(qkv, self.kcache[i][l], self.vcache[i][l], self.attn_ws[i],
+                                                                           self.hq, self.hkv, pos + 1, self.attn_splits))
                     continue
                 q, k, v = qkv.split([self.hq * D, self.hkv * D, self.hkv * D], dim=-1)
                 q = apply_rope(q.view(B, self.hq, D), posv, cfg.rope_theta)
@@ -187,17 +208,21 @@ class LlamaTP:
                 vv = self.vcache[i][l][:, :, :pos + 1]
                 o = F.scaled_dot_product_attention(q.unsqueeze(2), kk, vv, enable_gqa=self.hq != self.hkv)  # [B, hq, 1, D]
                 attn_out.append(o.reshape(B, self.hq * D))
-            normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo_run[i][l] for i in range(self.nlocal)])
+            with self._stage("o_proj_allreduce_norm"):
+                normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo_run[i][l] for i in range(self.nlocal)])
             act = []
             for i in range(self.nlocal):
-                gu = normed[i] @ self.wgu[i][l].t()
+                with self._stage("gate_up_gemm"):
+                    gu = normed[i] @ self.wgu[i][l].t()
                 if self.kernels:
-                    act.append(torch.ops.b200ipc.silu_mul(gu))
+                    with self._stage("silu_mul"):
+                        act.append(torch.ops.b200ipc.silu_mul(gu))
                     continue
                 gate, up = gu.split(self.ffn_local, dim=-1)
                 act.append(F.silu(gate) * up)
             gamma_next = self.norm_attn[l + 1] if l + 1 < cfg.layers else self.norm_final
-            normed, h = self._reduce_norm(h, gamma_next, act, [self.wdown_run[i][l] for i in range(self.nlocal)])
+            with self._stage("down_proj_allreduce_norm"):
+                normed, h = self._reduce_norm(h, gamma_next, act, [self.wdown_run[i][l] for i in range(self.nlocal)])
         self.last_hidden = normed  # final-norm output of every local rank (replicated values)
         # vocabulary-parallel head: local arg-max, then the global one over ranks
         best_val, best_idx = [], []

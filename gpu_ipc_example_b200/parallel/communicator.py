@@ -69,6 +69,8 @@ class Communicator:
         self.nlocal = self._C.nlocal(handle)
         self.rank = self._C.rank(handle, 0)
         self.last_info: Optional[CollInfo] = None
+        # largest input (bytes per rank) the one-shot all-reduce + residual + RMSNorm kernel is used for
+        self.fused_oneshot_max_bytes = 256 << 10
 
     # ------------------------------------------------------------------ creation
     @classmethod
@@ -87,7 +89,10 @@ class Communicator:
             job_id = os.environ.get("B200IPC_JOB_ID") or ("port" + os.environ["MASTER_PORT"] if "MASTER_PORT" in os.environ else "default")
         h = C.comm_create(rank, world, device, job_id, instance, staging_bytes, nvls, timeout_ms, backing, device_seq,
                           first_seq, max_ctas, bootstrap_timeout_ms)
-        return cls(h, False)
+        comm = cls(h, False)
+        if os.environ.get("B200IPC_SELFTEST", "0") not in ("", "0") and world > 1:
+            comm.self_test()  # falls back to the 8-byte-granule formats if a 64-byte segment is ever seen torn
+        return comm
 
     @classmethod
     def from_torch_distributed(cls, device: Optional[int] = None, **kw) -> "Communicator":
@@ -190,12 +195,25 @@ class Communicator:
 
     def allreduce_residual_rmsnorm(self, x: TensorOrList, residual: TensorOrList, gamma: TensorOrList, eps: float = 1e-5,
                                    *, ctas: int = 0):
-        """Returns (RMSNorm(all_reduce(x) + residual) * gamma, all_reduce(x) + residual) from one kernel."""
+        """Returns (RMSNorm(all_reduce(x) + residual) * gamma, all_reduce(x) + residual).
+
+        Decode-sized inputs (up to 256 KiB per rank) take ONE kernel: the one-shot flag-in-data exchange with the
+        add and the norm in its epilogue.  Larger ones (prefill) would push world - 1 copies of everything over the
+        links that way, so they take the bandwidth-optimal all-reduce of `auto` followed by one fused add + RMSNorm
+        kernel over the local result."""
         xs = self._lists(x)
         rs = self._lists(residual)
         gs = self._lists(gamma)
         xs2 = [t.reshape(-1, t.shape[-1]) for t in xs]
         rs2 = [t.reshape(-1, t.shape[-1]) for t in rs]
+        if xs2[0].numel() * xs2[0].element_size() > self.fused_oneshot_max_bytes and self.world > 1:
+            ins = [t.contiguous() for t in xs2]
+            summed = [torch.empty_like(t) for t in ins]  # x itself is left alone
+            self.all_reduce(ins if self._virtual else ins[0], summed if self._virtual else summed[0], "auto")
+            pairs = [torch.ops.b200ipc.add_rmsnorm(s, r.contiguous(), g.contiguous(), eps) for s, r, g in zip(summed, rs2, gs)]
+            outs = [p[0].view(t.shape) for p, t in zip(pairs, xs)]
+            res_outs = [p[1].view(t.shape) for p, t in zip(pairs, xs)]
+            return self._ret(x, outs), self._ret(x, res_outs)
         outs = [torch.empty_like(t) for t in xs2]
         res_outs = [torch.empty_like(t) for t in xs2]
         v = torch.ops.b200ipc.fused_ar_rmsnorm(xs2, rs2, gs, outs, res_outs, eps, self._h, ctas)
@@ -356,6 +374,57 @@ class Communicator:
     @property
     def seq(self) -> int:
         return self._C.seq(self._h)
+
+    # ------------------------------------------------------------------ protocol safety
+    def soak(self, algos=("simple_pcie_p", "simple", "small_pcie_p", "small"), min_transactions: int = 100000,
+             nelems: int = 1 << 20) -> dict:
+        """Bit-exact stress of the flag-in-data wire formats on this communicator's links: all-reduces of the
+        reference's integer pattern (i % 32) * (rank + 1) in fp16 (every partial sum exact), refilled before every
+        launch, until each algorithm has moved at least `min_transactions` warp transactions per rank; every
+        result element must equal the known sum exactly.  Returns {algo: {"transactions", "launches",
+        "mismatches"}}.  LL128 / LL512 (`simple*`) carry one flag per 64-byte segment and rely on such a segment
+        arriving whole - the assumption the reference flags at rt64_128.hpp:544; this is the test of it."""
+        i = torch.arange(nelems, device="cuda") % 32
+        world = self.world
+        want = (i * sum(r + 1 for r in range(world))).to(torch.float16)
+        ranks = [self._C.rank(self._h, k) for k in range(self.nlocal)]
+        pats = [(i * (r + 1)).to(torch.float16) for r in ranks]
+        report = {}
+        for algo in algos:
+            bad = torch.zeros((), dtype=torch.int64, device="cuda")
+            bufs = [torch.empty_like(p) for p in pats]
+            done = launches = 0
+            while done < min_transactions:
+                for b, p in zip(bufs, pats):
+                    b.copy_(p)
+                self.all_reduce(bufs if self._virtual else bufs[0], None, algo)
+                for b in bufs:
+                    bad += (b != want).sum()
+                done += int(self.last_info.steps) * int(self.last_info.nwires)
+                launches += 1
+            torch.cuda.synchronize()
+            self.check()
+            report[algo] = {"transactions": done, "launches": launches, "mismatches": int(bad)}
+        return report
+
+    def self_test(self, min_transactions: int = 20000) -> bool:
+        """Short soak of the two 64-byte-segment formats.  If a single element ever differs, `auto` stops using
+        them on this communicator (8-byte-granule formats only) and False is returned.  Collective."""
+        rep = self.soak(("simple_pcie_p", "simple"), min_transactions, nelems=1 << 18)
+        ok = all(v["mismatches"] == 0 for v in rep.values())
+        if self.world > 1 and not self._virtual:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                t = torch.tensor([0 if ok else 1], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ok = int(t.item()) == 0
+        self._C.set_safe_protos(self._h, not ok)
+        return ok
+
+    @property
+    def safe_protocols(self) -> bool:
+        return self._C.safe_protos(self._h)
 
     # ------------------------------------------------------------------ device-side trace
     def set_trace(self, on: bool = True):

@@ -5,7 +5,7 @@ import numpy as np
 
 from gpu_ipc_example_b200._ext import emulator_path
 
-OPS = {"parallel": 0, "sequential": 1, "ring": 2, "bisect": 3, "oneshot": 4, "ag_ring": 5, "ag_direct": 6}
+OPS = {"parallel": 0, "sequential": 1, "ring": 2, "bisect": 3, "oneshot": 4, "ag_ring": 5, "ag_direct": 6, "reduce_scatter": 7}
 PROTOS = {"LL8": 0, "LL16": 1, "LL128": 2, "LL512": 3}
 
 _lib = None

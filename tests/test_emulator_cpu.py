@@ -49,6 +49,41 @@ def test_allgather_is_rank_ordered_concatenation(world, op, proto):
             assert (o.view(np.uint16) == want.view(np.uint16)).all()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("proto", PROTOS)
+def test_reduce_scatter_back_to_back_on_the_same_rings(world, proto):
+    """Rank r ends with slice r of the sum.  A sender gets no reply in this schedule, so consecutive
+    launches alternate between the two halves of the ring (bit 1 of the sequence number)."""
+    L = emu.lib()
+    heaps = (ctypes.c_void_p * world)()
+    seq = 0xE00F100E
+    try:
+        for it, n in enumerate((8 * world, 960 * world, 2 * world * 777, 14336, 8 * world)):
+            ins = _inputs(world, n, seed=it)
+            outs = [np.zeros(n // world, np.float16) for _ in range(world)]
+            nwires = world * (3 if n > 2000 else 1)
+            payload = {"LL8": 32, "LL16": 64, "LL128": 30, "LL512": 120}[proto]
+            while -(-(n // world // 2) // ((nwires // world) * payload)) > 8:
+                nwires += world
+            rc, st = emu.run_threads(world, "reduce_scatter", proto, ins, outs, n, nwires, seq=seq, heaps=heaps)
+            assert rc == 0, st
+            want = np.sum(np.stack([x.astype(np.float32) for x in ins]), 0)
+            c = n // world
+            for r, o in enumerate(outs):
+                np.testing.assert_allclose(o.astype(np.float32), want[r * c:(r + 1) * c], atol=2e-2, rtol=4e-3)
+            assert L.b200emu_seq_advance(emu.OPS["reduce_scatter"], emu.PROTOS[proto], world, nwires, n) == 2
+            seq = (seq + 2) & 0xFFFFFFFF
+    finally:
+        L.b200emu_free_heaps(world, heaps)
+
+
+def test_reduce_scatter_refuses_more_steps_than_ring_slots():
+    ins = _inputs(2, 1 << 16)
+    outs = [np.zeros(1 << 15, np.float16) for _ in range(2)]
+    rc, _ = emu.run_threads(2, "reduce_scatter", "LL8", ins, outs, 1 << 16, 2)
+    assert rc == 2
+
+
 def test_in_place_and_pattern_exact():
     """(i % 32) * (rank + 1): the reference's verify pattern (utils.hpp:15-19); exact in fp16."""
     world, n = 8, 14336

@@ -83,3 +83,37 @@ def test_silu_mul(dtype):
     gate, up = gu.float().split(3584, dim=-1)
     tol = dict(atol=4e-3, rtol=4e-3) if dtype == torch.float16 else dict(atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(act.float(), F.silu(gate) * up, **tol)
+
+
+@pytest.mark.parametrize("dtype,hidden", [(torch.float16, 8192), (torch.bfloat16, 1024), (torch.float16, 8 * 4 * 256 + 64)])
+def test_add_rmsnorm(dtype, hidden):
+    load()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(37, hidden, device="cuda", generator=g).to(dtype)
+    r = torch.randn(37, hidden, device="cuda", generator=g).to(dtype)
+    gam = (torch.rand(hidden, device="cuda", generator=g) + 0.5).to(dtype)
+    out, res = torch.ops.b200ipc.add_rmsnorm(x, r, gam, 1e-5)
+    s = (x.float() + r.float()).to(dtype).float()
+    tol = dict(atol=1e-2, rtol=1e-2) if dtype == torch.float16 else dict(atol=6e-2, rtol=4e-2)
+    torch.testing.assert_close(res.float(), s, atol=0, rtol=0)
+    torch.testing.assert_close(out.float(), s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float(), **tol)
+
+
+def test_allreduce_residual_rmsnorm_prefill_sized():
+    """Above the one-shot limit the call becomes an all-reduce plus one fused add + RMSNorm kernel; same result."""
+    from gpu_ipc_example_b200 import Communicator
+
+    world, rows, hidden = 4, 512, 2048  # 2 MiB per rank
+    with Communicator.virtual(world, 0, staging_bytes=64 << 20) as comm:
+        g = torch.Generator(device="cuda").manual_seed(5)
+        parts = [torch.randn(rows, hidden, device="cuda", generator=g).half() for _ in range(world)]
+        keep = [p.clone() for p in parts]
+        res = torch.randn(rows, hidden, device="cuda", generator=g).half()
+        gam = (torch.rand(hidden, device="cuda", generator=g) + 0.5).half()
+        out, new_res = comm.allreduce_residual_rmsnorm(parts, [res] * world, [gam] * world, 1e-5)
+        torch.cuda.synchronize()
+        comm.check()
+        assert all(torch.equal(a, b) for a, b in zip(parts, keep)), "the inputs must not be modified"
+        s = (torch.stack([p.float() for p in parts]).sum(0).half().float() + res.float()).half().float()
+        torch.testing.assert_close(new_res[2].float(), s, atol=2e-2, rtol=4e-3)
+        torch.testing.assert_close(out[2].float(), s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float(), atol=3e-2, rtol=1e-2)

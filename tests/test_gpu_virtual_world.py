@@ -74,6 +74,30 @@ def test_allreduce_explicit_grids(comm, algo):
         _check_allreduce(comm, algo, 16384, torch.float16, ctas=ctas, warps=8)
 
 
+def test_reference_grid_matrix(comm):
+    """The reference's verify sweep (test/test_8tile_shapes.sh:4-19): group counts incl. odd ones x sub-group
+    counts x shapes with ragged tails, on the default algorithm and one of each other schedule.  A grid the
+    schedule cannot use (not a multiple of the world size, or more CTAs than can be resident at once) must be
+    refused with an error, never run."""
+    groups = (1, 2, 4, 8, 16, 32, 64, 7, 13, 15, 17, 19)
+    subgroups = (1, 2, 4, 8, 32)  # the reference's 64 sub-groups of 16 lanes are 32 warps here
+    shapes = (128, 256, 384, 1280, 1920, 1024, 2048, 14336, 16384)
+    ran = refused = 0
+    for algo in ("small", "simple", "simple_pcie", "simple_ring"):
+        k = 0
+        for g in groups:
+            for w in subgroups:
+                k += 1
+                n = shapes[k % len(shapes)]
+                try:
+                    _check_allreduce(comm, algo, n, torch.float16, ctas=g, warps=w)
+                    ran += 1
+                except RuntimeError as e:
+                    assert "multiple" in str(e) or "resident" in str(e) or "too many wires" in str(e), str(e)
+                    refused += 1
+    assert ran > 100 and ran + refused == 4 * len(groups) * len(subgroups)
+
+
 def test_grid_not_multiple_of_world_is_refused(comm):
     if comm.world == 2:
         pytest.skip("every even grid is a multiple of 2")
@@ -134,6 +158,40 @@ def test_reduce_scatter(comm):
         shard = n // comm.world
         for r, o in enumerate(outs):
             torch.testing.assert_close(o.float(), want[r * shard:(r + 1) * shard], atol=2e-2, rtol=4e-3)
+
+
+@pytest.mark.parametrize("algo", ["parallel:ll8", "parallel:ll16", "parallel:ll128", "parallel:ll512", "auto"])
+def test_reduce_scatter_flag_in_data_back_to_back(comm, algo):
+    """The flag-in-data reduce-scatter: a sender gets no reply, so launches alternate between the two
+    halves of the ring.  Many launches in a row without a host sync, sizes mixed."""
+    W = comm.world
+    sizes = [8 * W, 960 * W, 2 * W * 777, 8 * W * 4096, 8 * W]
+    cases = []
+    for rep in range(4):
+        for n in sizes:
+            xs = _inputs(W, n, torch.float16)
+            cases.append((xs, comm.reduce_scatter(xs, None, algo)))
+            if algo != "auto":
+                assert comm.last_info.sched == "parallel" and comm.last_info.launches == 1
+    torch.cuda.synchronize()
+    comm.check()
+    for xs, outs in cases:
+        want = torch.stack([x.float() for x in xs]).sum(0)
+        shard = want.numel() // W
+        for r, o in enumerate(outs):
+            torch.testing.assert_close(o.float(), want[r * shard:(r + 1) * shard], atol=2e-2, rtol=4e-3)
+
+
+def test_reduce_scatter_refuses_what_one_pass_cannot_hold(comm):
+    n = 8 * comm.world * (1 << 18)
+    xs = [torch.zeros(n, dtype=torch.float16, device="cuda") for _ in range(comm.world)]
+    with pytest.raises(RuntimeError, match="more than the"):
+        comm.reduce_scatter(xs, None, "parallel:ll8")
+    xs = [x[:n // 2] for x in xs]
+    outs = comm.reduce_scatter(xs, None, "auto")  # above 2 MiB auto takes the barrier-based kernel
+    torch.cuda.synchronize()
+    comm.check()
+    assert comm.last_info.sched in ("bulk", "nvls") and float(outs[0].abs().max()) == 0.0
 
 
 def test_symmetric_tensors_are_zero_copy(comm):

@@ -74,3 +74,23 @@ def test_in_place_and_refusals():
     assert _call(f, big, big, 0) == 2          # beyond the fixed scratch: refused, nothing launched
     three = [torch.zeros(64, device="cuda", dtype=torch.float16) for _ in range(3)]
     assert _call(f, three, three, 0) == 1      # world of 3 is not supported
+
+
+def test_a_silent_rank_is_reported_whichever_rank_notices(monkeypatch):
+    """A rank that sends nothing (test knob in the environment): some other rank's bounded wait runs out and
+    the ONE status record the caller gets back says so - whichever emulated rank was the first to notice."""
+    torch.cuda.set_device(0)
+    f = _entry()
+    monkeypatch.setenv("B200IPC_TIMEOUT_US", "50000")
+    monkeypatch.setenv("B200IPC_NOALLOC_MUTE_RANK", "0")  # rank 0 is the silent one: ranks 1..3 are the ones that time out
+    xs = [torch.ones(8192, device="cuda", dtype=torch.float16) for _ in range(4)]
+    outs = [torch.zeros_like(x) for x in xs]
+    status = (ctypes.c_uint32 * 8)()
+    assert _call(f, xs, outs, 0, status) == 0
+    torch.cuda.synchronize()
+    assert status[0] in (1, 2), list(status)   # timed out, or told to stop by the one that did
+    monkeypatch.delenv("B200IPC_NOALLOC_MUTE_RANK")
+    status2 = (ctypes.c_uint32 * 8)()
+    assert _call(f, xs, outs, 0, status2) == 0  # the next call clears the control words and works again
+    torch.cuda.synchronize()
+    assert status2[0] == 0 and float(outs[2][5]) == 4.0
