@@ -442,7 +442,16 @@ int run_rank(int rank, int world, const Options& opt_in, UnixMesh* mesh) {
 
       fill_inputs(true);
       comm->host_barrier();
-      CollInfo info = launch_once(0);
+      CollInfo info;
+      try {
+        info = launch_once(0);
+      } catch (const std::exception& e) {
+        // a geometry this algorithm does not take at this size: the check runs on the host before anything is
+        // launched and depends on nothing but the size, so every rank skips the same rows
+        if (rank == 0) std::printf("# skipped %zu elements: %s\n", n, e.what());
+        cudaGetLastError();
+        continue;
+      }
       B200_CUDA_CHECK(cudaStreamSynchronize(stream));
       comm->raise_if_failed();
 

@@ -1,5 +1,7 @@
 #include "comm.h"
 
+#include "../common/pdl.h"
+
 #include <algorithm>
 #include <cctype>
 #include <cstdlib>
@@ -308,26 +310,19 @@ int Comm::resident_ctas(KernelFn fn, int threads, size_t smem) {
   return total;
 }
 
-void Comm::launch(KernelFn fn, int ctas, int threads, KArgs* args, size_t smem, cudaStream_t stream) {
+void Comm::launch(KernelFn fn, int ctas, int threads, KArgs* args, size_t smem, cudaStream_t stream, bool pdl) {
   void* params[] = {args};
+  launch_raw(reinterpret_cast<const void*>(fn), ctas, threads, params, smem, stream, pdl);
+}
+
+void Comm::launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream, bool pdl) {
   dim3 grid(unsigned(ctas), unsigned(nlocal()), 1);
   dim3 block(unsigned(threads), 1, 1);
   if (nlocal() > 1) {
     // ranks wait on each other inside the kernel: all block rows must be resident
-    B200_CUDA_CHECK(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fn), grid, block, params, smem, stream));
-  } else {
-    B200_CUDA_CHECK(cudaLaunchKernel(reinterpret_cast<const void*>(fn), grid, block, params, smem, stream));
-  }
-  ++launches_;
-}
-
-void Comm::launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream) {
-  dim3 grid(unsigned(ctas), unsigned(nlocal()), 1);
-  dim3 block(unsigned(threads), 1, 1);
-  if (nlocal() > 1) {
     B200_CUDA_CHECK(cudaLaunchCooperativeKernel(fn, grid, block, params, smem, stream));
   } else {
-    B200_CUDA_CHECK(cudaLaunchKernel(fn, grid, block, params, smem, stream));
+    B200_CUDA_CHECK(launch_maybe_pdl(fn, grid, block, params, smem, stream, pdl));
   }
   ++launches_;
 }
@@ -717,11 +712,12 @@ CollInfo Comm::reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, vo
   if (algo.automatic) {
     algo = AlgoSpec{};
     // small inputs: one flag-in-data push to each slice's owner, no barrier
-    if (nelems % (2 * size_t(world_)) == 0 && nelems * 2 <= kReduceScatterLLMaxBytes) {
+    if (nelems % (2 * size_t(world_)) == 0 && nelems * 2 <= (safe_protos_ ? kReduceScatterLLMaxBytes / 2 : kReduceScatterLLMaxBytes)) {
       algo.sched = SchedKind::Parallel;
       algo.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
     } else {
-      algo.sched = has_nvls() ? SchedKind::Nvls : SchedKind::Bulk;
+      // two ranks: peer loads beat the in-switch reduction (nothing to reduce in the switch with one peer)
+      algo.sched = (has_nvls() && world_ > 2) ? SchedKind::Nvls : SchedKind::Bulk;
     }
   }
   if (algo.sched == SchedKind::Parallel)

@@ -68,9 +68,11 @@ struct CommOptions {
   int max_ctas = 0;         // cap on CTAs per launch (0 = fill the GPU)
 };
 
-// Largest input (bytes) that `auto` gives to the flag-in-data reduce-scatter: a launch takes at
-// most kParallelSlots steps, and this much fits in them at the default geometry with every proto.
-constexpr size_t kReduceScatterLLMaxBytes = size_t(2) << 20;
+// Largest input (bytes) that `auto` gives to the flag-in-data reduce-scatter: a launch takes at most
+// kParallelSlots steps, and 8 MiB fit in them at the default geometry with the 512-byte format (half of
+// that with the 8-byte-granule fallback).  Measured on two B200s: ahead of the barrier-based kernel and of
+// NCCL at every size up to there (8 MiB: 16.5 us against 26.1 and 29.3).
+constexpr size_t kReduceScatterLLMaxBytes = size_t(8) << 20;
 
 class Comm {
  public:
@@ -145,12 +147,14 @@ class Comm {
 
   // Launch plumbing shared with the fused ops.
   void fill_views(KArgs* args, const void* const* ins, void* const* outs, size_t nelems, uint32_t flags) const;
-  void launch(KernelFn fn, int ctas, int threads, KArgs* args, size_t smem, cudaStream_t stream);
+  void launch(KernelFn fn, int ctas, int threads, KArgs* args, size_t smem, cudaStream_t stream, bool pdl = false);
   int resident_ctas(KernelFn fn, int threads, size_t smem);
   uint32_t take_seq(uint32_t advance);
   uint32_t take_barrier();
   // Launch with caller-built parameters (cooperative when this communicator drives several ranks).
-  void launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream);
+  // pdl: the kernel executes griddepcontrol.wait before it touches anything an earlier kernel wrote, so it may be
+  // launched with programmatic stream serialisation (single-rank launches only; see common/pdl.h)
+  void launch_raw(const void* fn, int ctas, int threads, void** params, size_t smem, cudaStream_t stream, bool pdl = false);
   // Running total of the delivery counter of the fused GEMM kernels: returns the value the
   // counter reaches after `inc` more deliveries.
   uint32_t take_done(uint32_t inc) {

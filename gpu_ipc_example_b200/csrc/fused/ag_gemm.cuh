@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) ag_gemm_kernel(const __grid_c
   extern __shared__ unsigned char smem_raw[];
   using Smem = GemmSmem<BN, STAGES, kGemmBM>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  pdl_launch_dependents();
+  pdl_wait();  // activations, flags and counters come from earlier kernels
 
   const RankView& me = args.k.v[blockIdx.y];
   const HeapLayout& lay = args.k.lay;

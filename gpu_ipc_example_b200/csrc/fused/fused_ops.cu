@@ -73,7 +73,7 @@ CollInfo fused_allreduce_residual_rmsnorm(Comm& comm, DType t, const FusedNormPt
     args.v[i].aux[2] = reinterpret_cast<uint64_t>(ptrs[i].residual_out);
     args.v[i].aux[3] = uint64_t(uint32_t(hidden)) | (uint64_t(float_bits(eps)) << 32);
   }
-  comm.launch(fn, ctas, threads, &args, 0, stream);
+  comm.launch(fn, ctas, threads, &args, 0, stream, true);
   CollInfo info;
   info.sched = SchedKind::OneShot;
   info.proto = ProtoKind::LL512;
@@ -120,7 +120,7 @@ CollInfo fused_allreduce_scale_cast(Comm& comm, DType tin, DType tout, const voi
     B200_REQUIRE((reinterpret_cast<uintptr_t>(ins[i]) & 3) == 0 && (reinterpret_cast<uintptr_t>(outs[i]) & 3) == 0,
                  "buffers must be 4-byte aligned");
   }
-  comm.launch(fn, ctas, threads, &args, 0, stream);
+  comm.launch(fn, ctas, threads, &args, 0, stream, true);
   CollInfo info;
   info.sched = SchedKind::OneShot;
   info.proto = ProtoKind::LL512;

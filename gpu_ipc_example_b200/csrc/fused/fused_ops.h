@@ -48,8 +48,10 @@ struct GemmArWorkspace {
   size_t total() const { return landing_bytes + flags_bytes + inv_bytes; }
 };
 GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N);
+// local_only: no exchange, out = this rank's own x @ w^T (the weight-streaming kernel for M <= 32 rows as a plain
+// GEMM: column-parallel projections of a decode step); needs M <= 32 and N a multiple of 128.
 CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
-                              bool with_norm, int ctas, cudaStream_t stream);
+                              bool with_norm, int ctas, cudaStream_t stream, bool local_only = false);
 
 // All-gather of row-sharded activations fused with the GEMM that consumes them: see ag_gemm.cuh.
 struct AgGemmPtrs {

@@ -102,7 +102,7 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
 
 // Decode sizes (M <= 32, N a multiple of 128): the swapped-operand, split-K kernel of gemm_decode.cuh.
 static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
-                                  bool with_norm, int ctas_req, cudaStream_t stream) {
+                                  bool with_norm, int ctas_req, cudaStream_t stream, bool local_only) {
   const int W = comm.world();
   const void* fn = t == DType::F16 ? reinterpret_cast<const void*>(&gemm_decode_kernel<__half>)
                                    : reinterpret_cast<const void*>(&gemm_decode_kernel<__nv_bfloat16>);
@@ -168,6 +168,7 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
   args.rows_per_rank = int(splits);
   args.eps = eps;
   args.with_norm = with_norm ? 1 : 0;
+  args.local_only = local_only ? 1 : 0;
   args.landing_off = landing_off;
   args.flags_off = landing_off + ws.landing_bytes;
   args.inv_off = args.flags_off + ws.flags_bytes;
@@ -183,7 +184,7 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
     args.k.v[i].seq_step = adv;
   }
   void* params[] = {&args};
-  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream, true);
   CollInfo info;
   info.sched = SchedKind::OneShot;
   info.proto = ProtoKind::LL512;
@@ -197,7 +198,7 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
 }
 
 CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64_t M, int64_t N, int64_t K, float eps,
-                              bool with_norm, int ctas_req, cudaStream_t stream) {
+                              bool with_norm, int ctas_req, cudaStream_t stream, bool local_only) {
   const int W = comm.world();
   B200_REQUIRE(M > 0 && N > 0 && K > 0, "empty GEMM");
   B200_REQUIRE(N % 64 == 0, "N must be a multiple of 64");
@@ -205,8 +206,14 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   B200_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, "world size must be 1, 2, 4 or 8");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
   const int mode = gemm_mode_for(M, with_norm, ptrs[0].residual != nullptr && ptrs[0].res_out != nullptr);
+  if (local_only) {
+    B200_REQUIRE(M <= kDecXRows && N % kDecTileRows == 0 && !with_norm && ptrs[0].residual == nullptr,
+                 "the local (no exchange) form takes M <= " << kDecXRows << " rows, N a multiple of " << kDecTileRows
+                                                           << ", no residual and no norm");
+    return fused_gemm_decode(comm, t, ptrs, M, N, K, eps, false, ctas_req, stream, true);
+  }
   if (mode == kGemmModeOneShot && N % kDecTileRows == 0 && std::getenv("B200IPC_GEMM_NO_SWAP") == nullptr)
-    return fused_gemm_decode(comm, t, ptrs, M, N, K, eps, with_norm, ctas_req, stream);
+    return fused_gemm_decode(comm, t, ptrs, M, N, K, eps, with_norm, ctas_req, stream, false);
   // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
   // cut the operand traffic per FLOP for large M.
   const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
@@ -330,7 +337,7 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
   }
 
   void* params[] = {&args};
-  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream, true);
 
   CollInfo info;
   info.sched = mode == kGemmModeOneShot ? SchedKind::OneShot : SchedKind::Bulk;
@@ -416,7 +423,7 @@ CollInfo fused_allgather_gemm(Comm& comm, DType t, const AgGemmPtrs* ptrs, int64
   args.K = int(K);
   args.rows_per_rank = int(M / W);
   void* params[] = {&args};
-  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream);
+  comm.launch_raw(fn, ctas, kGemmThreads, params, smem, stream, true);
   CollInfo info;
   info.sched = SchedKind::Bulk;
   info.proto = ProtoKind::LL512;

@@ -72,6 +72,7 @@ struct GemmArArgs {
   uint32_t epoch;        // launch number of this kernel family on the communicator: the flag value
   float eps;
   int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
+  int local_only;        // 1: no exchange at all, out = this rank's own product (decode-sized kernel only)
   // heap offsets (same on every rank)
   uint64_t landing_off;  // reduce-scatter: [world][rows_per_rank][N] partials from every source; one-shot: [M][N], this rank's own
   uint64_t flags_off;    // reduce-scatter: [world][m_tiles][n_tiles][4]; one-shot: [n_tiles]   uint32
@@ -425,6 +426,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_ar_kernel(const __grid_c
   extern __shared__ unsigned char smem_raw[];
   using Smem = GemmSmem<BN, STAGES, A_ROWS, KSUB>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  pdl_launch_dependents();
+  pdl_wait();  // activations, flags and counters come from earlier kernels
 
   const RankView& me = args.k.v[blockIdx.y];
   const HeapLayout& lay = args.k.lay;

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_decode_kernel(const __gr
 
   const RankView& me = args.k.v[blockIdx.y];
   const HeapLayout& lay = args.k.lay;
-  const int W = me.world;
+  const int W = args.local_only ? 1 : me.world;
   const int rank = me.rank;
   const int warp = int(threadIdx.x >> 5);
   const int lane = int(threadIdx.x & 31);
@@ -65,8 +65,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_decode_kernel(const __gr
   int kb_per = (kb_total + splits - 1) / splits;
   kb_per = (kb_per + kDecKSub - 1) / kDecKSub * kDecKSub;
   const uint64_t timeout_ns = me.timeout_ns;
-  uint32_t epoch = args.epoch;
-  if (me.seq_dev) epoch += ld_volatile_u32(me.seq_dev + kGemmEpochSlot);
+  pdl_launch_dependents();  // the next kernel may set itself up (and prefetch its weights) while this one runs
   constexpr uint32_t kTmemCols = 2 * kDecXRows;
   constexpr uint32_t kSubBytes = uint32_t(kDecTileRows + kDecXRows) * kGemmBK * 2;
 
@@ -95,12 +94,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_decode_kernel(const __gr
   volatile int* abort_flag = &s.abort_flag;
   if (threadIdx.x == 0) gemm_trace(me, lay, 1);
 
+  const CUtensorMap* tx = &args.tma_a[blockIdx.y];
+  const CUtensorMap* tw = &args.tma_b[blockIdx.y];
+  const char* wp = static_cast<const char*>(args.w_packed[blockIdx.y]);
+  constexpr uint32_t kBlk = 64 * kGemmBK * 2;
+  auto load_w = [&](int st, int sub, int tile, int kb) {
+    if (wp) {
+      for (int rb = 0; rb < kDecTileRows / 64; ++rb)
+        bulk_load(s.a[st][sub] + rb * kBlk,
+                  wp + (size_t(tile * (kDecTileRows / 64) + rb) * size_t(args.packed_kblocks) + size_t(kb)) * kBlk, kBlk, &s.full[st]);
+    } else {
+      tma_load_2d(s.a[st][sub], tw, &s.full[st], kb * kGemmBK, tile * kDecTileRows);
+    }
+  };
+  // The weights do not depend on the kernel before this one: the producer fills the ring with the W halves of
+  // its first stages before it waits for that kernel; the X halves follow after the wait.
+  uint32_t npre = 0;
+  if (warp == 0 && lane == 0 && int(blockIdx.x) < units) {
+    const int u = int(blockIdx.x);
+    const int tile = u / splits, ks = u % splits;
+    const int kb0 = ks * kb_per;
+    int kb1 = kb0 + kb_per;
+    if (kb1 > kb_total) kb1 = kb_total;
+    for (int kb = kb0; kb < kb1 && npre < uint32_t(kDecStages); kb += kDecKSub, ++npre) {
+      const int nsub = (kb1 - kb) < kDecKSub ? (kb1 - kb) : kDecKSub;
+      mbar_expect_tx(&s.full[npre], kSubBytes * uint32_t(nsub));
+      for (int sub = 0; sub < nsub; ++sub) load_w(int(npre), sub, tile, kb + sub);
+    }
+  }
+  pdl_wait();  // everything below may read what earlier kernels wrote (activations, flags, counters, the fp32 product)
+  uint32_t epoch = args.epoch;
+  if (me.seq_dev) epoch += ld_volatile_u32(me.seq_dev + kGemmEpochSlot);
+
   if (warp == 0) {
     if (lane == 0) {
-      const CUtensorMap* tx = &args.tma_a[blockIdx.y];
-      const CUtensorMap* tw = &args.tma_b[blockIdx.y];
-      const char* wp = static_cast<const char*>(args.w_packed[blockIdx.y]);
-      constexpr uint32_t kBlk = 64 * kGemmBK * 2;
       uint32_t it = 0;
       for (int u = int(blockIdx.x); u < units && !*abort_flag; u += G) {
         const int tile = u / splits, ks = u % splits;
@@ -110,19 +137,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_decode_kernel(const __gr
         for (int kb = kb0; kb < kb1; kb += kDecKSub, ++it) {
           const int st = int(it % kDecStages);
           const uint32_t ph = (it / kDecStages) & 1u;
-          if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, timeout_ns)) break;
           const int nsub = (kb1 - kb) < kDecKSub ? (kb1 - kb) : kDecKSub;
-          mbar_expect_tx(&s.full[st], kSubBytes * uint32_t(nsub));
+          const bool w_done = it < npre;  // this stage's W halves are already on their way
+          if (!w_done) {
+            if (!mbar_wait(&s.empty[st], ph ^ 1u, abort_flag, timeout_ns)) break;
+            mbar_expect_tx(&s.full[st], kSubBytes * uint32_t(nsub));
+          }
           for (int sub = 0; sub < nsub; ++sub) {
             tma_load_2d(s.b[st][sub], tx, &s.full[st], (kb + sub) * kGemmBK, 0);
-            if (wp) {
-              for (int rb = 0; rb < kDecTileRows / 64; ++rb)
-                bulk_load(s.a[st][sub] + rb * kBlk,
-                          wp + (size_t(tile * (kDecTileRows / 64) + rb) * size_t(args.packed_kblocks) + size_t(kb + sub)) * kBlk, kBlk,
-                          &s.full[st]);
-            } else {
-              tma_load_2d(s.a[st][sub], tw, &s.full[st], (kb + sub) * kGemmBK, tile * kDecTileRows);
-            }
+            if (!w_done) load_w(st, sub, tile, kb + sub);
           }
         }
       }

@@ -13,6 +13,7 @@
 #pragma once
 
 #include "../coll/schedules.h"
+#include "../common/pdl.h"
 #include "../proto/dev_backend.cuh"
 
 namespace b200ipc {
@@ -49,7 +50,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
                                                    float* s_part, int* s_abort_p, bool advance_seq_dev) {
   using B = DevBackend<ProtoKind::LL512, T>;
   int& s_abort = *s_abort_p;
-  const int r = me.rank;
+  const int r = N == 1 ? 0 : me.rank;  // N == 1: no exchange at all (a rank of a larger world may run the body alone)
   const int lane = int(threadIdx.x & 31);
   const int warp = int(threadIdx.x >> 5);
   const int warps = int(blockDim.x >> 5);
@@ -363,6 +364,8 @@ template <typename T, typename Tout, int N, int EPI>
 __global__ void __launch_bounds__(kFusedMaxThreads) oneshot_fused_kernel(const __grid_constant__ KArgs args) {
   __shared__ float s_part[32];
   __shared__ int s_abort;
+  pdl_launch_dependents();
+  pdl_wait();  // the input is the previous kernel's output
   const RankView& me = args.v[blockIdx.y];
   FusedOperands op;
   op.in = me.in;

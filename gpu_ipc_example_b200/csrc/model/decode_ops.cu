@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 
 #include "../common/check.h"
+#include "../common/pdl.h"
 
 namespace b200ipc {
 namespace {
@@ -32,14 +33,33 @@ struct Num<__nv_bfloat16> {
   __device__ static T2 down(float a, float b) { return __floats2bfloat162_rn(a, b); }
 };
 
+// Every kernel of this file starts with pdl_launch_dependents() + pdl_wait() and is launched with programmatic
+// stream serialisation: its CTAs can be resident before the previous kernel of the step has drained.
+template <typename... Params, typename... Args>
+void launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1u : 0u;
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+}
+
 // ---------------------------------------------------------------------------------------------
 // RoPE + cache append.  qkv: [B, (hq + 2 hkv) * D] as the QKV projection leaves it.  Rotates q in
 // place (pairs (i, i + D/2)), writes the rotated k and the v of the new position into the caches
 // [B, hkv, max_ctx, D] at `pos`.  One CTA per (batch row, head), one thread per pair.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_kv_append_kernel(T* __restrict__ qkv, T* __restrict__ kcache, T* __restrict__ vcache, int hq, int hkv, int D,
+__global__ void rope_kv_append_kernel(T* qkv, T* kcache, T* vcache, int hq, int hkv, int D,
                                       int max_ctx, int pos, float log2_theta) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   const int head = blockIdx.y;  // 0..hq-1: q, hq..hq+hkv-1: k, then v
   const int half = D / 2;
@@ -70,131 +90,203 @@ __global__ void rope_kv_append_kernel(T* __restrict__ qkv, T* __restrict__ kcach
 
 // ---------------------------------------------------------------------------------------------
 // Decode attention, head_dim 128, G = hq / hkv query heads per KV head (1, 2, 4 or 8).
-// Grid (splits, hkv, B), 128 threads.  A warp walks its share of the context four positions at a
-// time: for the scores eight lanes share a position (16 elements of the 256-byte K row each, two
-// 16-byte loads, so a warp instruction reads 1 KiB of contiguous cache); for the weighted sum a lane
-// owns 4 of the 128 dimensions of every position.  Online softmax per head in fp32.  Warps merge in
-// shared memory, splits through a workspace; the last CTA of a (batch, KV head) to arrive writes
-// the result.
+// Grid (splits, hkv, B), 128 threads.  A warp walks its share of the context 16 positions at a
+// time on the warp-level tensor path (mma.sync m16n8k16, fp32 accumulation); the cache goes
+// from global memory straight into the operand registers with 16-byte loads, nothing is staged:
+//
+//   scores   S[head, pos] = Q K^T : A = Q (rows = the G heads, zero-padded to 16), B = K^T.  The
+//            contraction index may be permuted as long as A and B agree, so the lane (r, c) =
+//            (lane / 4, lane % 4) simply loads the 16-byte chunks c, c+4, c+8, c+12 of "its" row
+//            (Q: head r, K: position r of the 8-position tile) and word 2k / 2k+1 of those 16
+//            words feeds step k.
+//   softmax  online, in the log2 domain, per head; a quad (the 4 lanes of one head) shares the max.
+//   output   O^T[dim, head] = V^T P^T : B = P^T is exactly the register layout S came out in; for
+//            A = V^T the lane loads 32 contiguous bytes (dims 16r .. 16r+15) of the four positions
+//            2c, 2c+1, 2c+8, 2c+9 and a byte-permute pairs the same dimension of two positions.
+//            Output rows are permuted so that the lane ends up with dims 16r .. 16r+15 of heads
+//            2c and 2c+1.
+//
+// Warps merge in shared memory, splits through a workspace; the last CTA of a (batch, KV head)
+// to arrive writes the result.
 // ---------------------------------------------------------------------------------------------
 constexpr int kAttnD = 128;
 constexpr int kAttnThreads = 128;
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnTile = 16;  // positions per warp step
+
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                  uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const typename Num<T>::T2 v = Num<T>::down(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// 16 words of a 256-byte row: the 16-byte chunks c, c+4, c+8, c+12
+template <typename T>
+__device__ __forceinline__ void load_row_quarter(uint32_t (&w)[16], const T* row, int c) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 x = *reinterpret_cast<const uint4*>(row + (c + 4 * i) * 8);
+    w[4 * i + 0] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+  }
+}
 
 template <typename T, int G>
-__global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ kcache,
-                                                                        const T* __restrict__ vcache, T* __restrict__ out,
-                                                                        float* __restrict__ part, unsigned int* __restrict__ counters,
+__global__ void __launch_bounds__(kAttnThreads, 2) decode_attention_kernel(const T* q, const T* kcache, const T* vcache, T* out,
+                                                                           float* part, unsigned int* counters,
                                                                         int hq, int hkv, int max_ctx, int ctx, int q_row_stride,
                                                                         float scale_log2) {
   using T2 = typename Num<T>::T2;
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, nsplit = gridDim.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int grp = lane >> 3, sub = lane & 7;  // score phase: position within the four, 16-element slice of the row
+  const int r = lane >> 2, c = lane & 3;
 
-  // the G query rows, pre-scaled by softmax scale * log2(e), in shared memory: [head][16-element slice][16 + 4 pad]
-  // (the pad spreads the eight slices over all banks; the four lanes that share a slice read one address)
-  __shared__ __align__(16) float s_q[G][8][20];
-  for (int i = threadIdx.x; i < G * kAttnD; i += kAttnThreads) {
-    const int g = i / kAttnD, d = i % kAttnD;
-    s_q[g][d / 16][d % 16] = float(q[size_t(b) * q_row_stride + (size_t(h) * G + g) * kAttnD + d]) * scale_log2;
-  }
-  __syncthreads();
-
-  float m[G], l[G], o[G][4];
+  // Q operand: head r of this KV head's group (rows G..15 of the 16-row operand are zero)
+  uint32_t qa[16];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-    o[g][0] = o[g][1] = o[g][2] = o[g][3] = 0.f;
-  }
+  for (int i = 0; i < 16; ++i) qa[i] = 0u;
+  if (r < G) load_row_quarter<T>(qa, q + size_t(b) * q_row_stride + (size_t(h) * G + r) * kAttnD, c);
 
-  const int per = (ctx + nsplit - 1) / nsplit;
+  // running state of head r (every lane of the quad holds the same m; l is a per-lane partial sum)
+  float m = -INFINITY, l = 0.f;
+  // O^T: acc[t][0..3] = (dim 16r+2t, head 2c), (dim 16r+2t, head 2c+1), (dim 16r+2t+1, head 2c), (dim 16r+2t+1, head 2c+1)
+  float acc[8][4];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+
+  const int per = ((ctx + nsplit - 1) / nsplit + kAttnTile - 1) / kAttnTile * kAttnTile;  // whole tiles per split
   const int p0 = split * per;
-  const int p1 = min(p0 + per, ctx);
+  const int p1 = min(p0 + per, ctx);  // may be <= p0: a split without work contributes an empty state
   const T* kb = kcache + (size_t(b) * hkv + h) * size_t(max_ctx) * kAttnD;
   const T* vb = vcache + (size_t(b) * hkv + h) * size_t(max_ctx) * kAttnD;
 
-  for (int base = p0 + warp * 4; base < p1; base += kAttnWarps * 4) {
-    const int p = base + grp;
-    float s[G];
+  // one step's operands: K rows of positions base + r and base + 8 + r, V of the four positions 2c, 2c+1, 2c+8, 2c+9
+  auto load_tile = [&](int base, uint32_t (&kw)[2][16], uint32_t (&vw)[4][8]) {
 #pragma unroll
-    for (int g = 0; g < G; ++g) s[g] = 0.f;
-    if (p < p1) {
-      const uint4 a = *reinterpret_cast<const uint4*>(kb + size_t(p) * kAttnD + sub * 16);
-      const uint4 c = *reinterpret_cast<const uint4*>(kb + size_t(p) * kAttnD + sub * 16 + 8);
-      const T2* pa = reinterpret_cast<const T2*>(&a);
-      const T2* pc = reinterpret_cast<const T2*>(&c);
-      float2 kf[8];
+    for (int j = 0; j < 2; ++j) {
+      const int p = base + 8 * j + r;
+      if (p < p1) {
+        load_row_quarter<T>(kw[j], kb + size_t(p) * kAttnD, c);
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        kf[e] = Num<T>::up(pa[e]);
-        kf[4 + e] = Num<T>::up(pc[e]);
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float4* qv = reinterpret_cast<const float4*>(&s_q[g][sub][0]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float4 qq = qv[e];
-          s[g] = fmaf(qq.x, kf[2 * e].x, fmaf(qq.y, kf[2 * e].y, fmaf(qq.z, kf[2 * e + 1].x, fmaf(qq.w, kf[2 * e + 1].y, s[g]))));
-        }
-      }
-    }
-    // the eight lanes of a position add their slices
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-      s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
-      s[g] += __shfl_xor_sync(0xffffffffu, s[g], 4);
-      if (p >= p1) s[g] = -INFINITY;
-    }
-    // V rows of the four positions: a lane owns dimensions 4 * lane .. + 3
-    float4 vf[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      vf[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (base + j < p1) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(vb + size_t(base + j) * kAttnD + lane * 4);
-        const float2 lo = Num<T>::up(*reinterpret_cast<const T2*>(&raw.x));
-        const float2 hi = Num<T>::up(*reinterpret_cast<const T2*>(&raw.y));
-        vf[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
+        for (int i = 0; i < 16; ++i) kw[j][i] = 0u;
       }
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      // scores of the four positions to every lane
-      float sj[4];
+    for (int x = 0; x < 4; ++x) {
+      const int p = base + 2 * c + (x & 1) + 8 * (x >> 1);
+      if (p < p1) {
+        const uint4 lo = *reinterpret_cast<const uint4*>(vb + size_t(p) * kAttnD + 16 * r);
+        const uint4 hi = *reinterpret_cast<const uint4*>(vb + size_t(p) * kAttnD + 16 * r + 8);
+        vw[x][0] = lo.x; vw[x][1] = lo.y; vw[x][2] = lo.z; vw[x][3] = lo.w;
+        vw[x][4] = hi.x; vw[x][5] = hi.y; vw[x][6] = hi.z; vw[x][7] = hi.w;
+      } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sj[j] = __shfl_sync(0xffffffffu, s[g], j * 8);
-      const float mx = fmaxf(fmaxf(sj[0], sj[1]), fmaxf(sj[2], sj[3]));
-      const float mnew = fmaxf(m[g], mx);  // finite: position `base` always exists
-      const float corr = exp2f(m[g] - mnew);
-      m[g] = mnew;
-      float pj[4];
+        for (int i = 0; i < 8; ++i) vw[x][i] = 0u;
+      }
+    }
+  };
+  auto compute_tile = [&](int base, const uint32_t (&kw)[2][16], const uint32_t (&vw)[4][8]) {
+    // ---- scores: s[j][0..1] = head r, positions base + 8j + 2c, + 1 --------------------------------
+    float s[2][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) pj[j] = exp2f(sj[j] - mnew);
-      l[g] = l[g] * corr + (pj[0] + pj[1]) + (pj[2] + pj[3]);
-      o[g][0] = o[g][0] * corr + pj[0] * vf[0].x + pj[1] * vf[1].x + pj[2] * vf[2].x + pj[3] * vf[3].x;
-      o[g][1] = o[g][1] * corr + pj[0] * vf[0].y + pj[1] * vf[1].y + pj[2] * vf[2].y + pj[3] * vf[3].y;
-      o[g][2] = o[g][2] * corr + pj[0] * vf[0].z + pj[1] * vf[1].z + pj[2] * vf[2].z + pj[3] * vf[3].z;
-      o[g][3] = o[g][3] * corr + pj[0] * vf[0].w + pj[1] * vf[1].w + pj[2] * vf[2].w + pj[3] * vf[3].w;
+    for (int j = 0; j < 2; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mma_16816<T>(s[j], qa[2 * k], 0u, qa[2 * k + 1], 0u, kw[j][2 * k], kw[j][2 * k + 1]);
+    }
+    float sc[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) sc[2 * j + e] = (base + 8 * j + 2 * c + e < p1) ? s[j][e] * scale_log2 : -INFINITY;
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mnew = fmaxf(m, mx);  // finite: position `base` exists
+    const float corr = exp2f(m - mnew);
+    m = mnew;
+    float pr[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pr[e] = exp2f(sc[e] - mnew);
+    l = l * corr + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+    const uint32_t pb0 = pack2<T>(pr[0], pr[1]), pb1 = pack2<T>(pr[2], pr[3]);
+    // the accumulator columns of this lane belong to heads 2c and 2c+1, whose state lives in quads 2c and 2c+1
+    const float corr0 = __shfl_sync(0xffffffffu, corr, 8 * c);
+    const float corr1 = __shfl_sync(0xffffffffu, corr, 8 * c + 4);
+    // ---- O^T += V^T P^T --------------------------------------------------------------------------
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      acc[t][0] *= corr0; acc[t][1] *= corr1; acc[t][2] *= corr0; acc[t][3] *= corr1;
+      const uint32_t a0 = __byte_perm(vw[0][t], vw[1][t], 0x5410);  // dim 16r+2t   of positions 2c, 2c+1
+      const uint32_t a1 = __byte_perm(vw[0][t], vw[1][t], 0x7632);  // dim 16r+2t+1 of positions 2c, 2c+1
+      const uint32_t a2 = __byte_perm(vw[2][t], vw[3][t], 0x5410);  // ... of positions 2c+8, 2c+9
+      const uint32_t a3 = __byte_perm(vw[2][t], vw[3][t], 0x7632);
+      mma_16816<T>(acc[t], a0, a1, a2, a3, pb0, pb1);
+    }
+  };
+  // two register sets: the loads of the next step are in flight while this one is computed
+  {
+    const int stride = kAttnWarps * kAttnTile;
+    uint32_t kA[2][16], vA[4][8], kB[2][16], vB[4][8];
+    int base = p0 + warp * kAttnTile;
+    if (base < p1) load_tile(base, kA, vA);
+    while (base < p1) {
+      const int nb = base + stride;
+      if (nb < p1) load_tile(nb, kB, vB);
+      compute_tile(base, kA, vA);
+      if (nb >= p1) break;
+      base = nb + stride;
+      if (base < p1) load_tile(base, kA, vA);
+      compute_tile(nb, kB, vB);
     }
   }
+  // the quad's partial sums of l
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
 
   // ---- merge the warps of the CTA -----------------------------------------------------------
   __shared__ float s_m[kAttnWarps][G], s_l[kAttnWarps][G];
-  __shared__ float4 s_o[kAttnWarps][G][32];
+  __shared__ __align__(16) float4 s_o[kAttnWarps][G][32];
   __shared__ int s_last;
+  if (c == 0 && r < G) {
+    s_m[warp][r] = m;
+    s_l[warp][r] = l;
+  }
+  {
+    float* so = reinterpret_cast<float*>(&s_o[warp][0][0]);  // [head][dim]
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      s_m[warp][g] = m[g];
-      s_l[warp][g] = l[g];
+    for (int t = 0; t < 8; ++t) {
+      if (2 * c < G) {
+        so[(2 * c) * kAttnD + 16 * r + 2 * t] = acc[t][0];
+        so[(2 * c) * kAttnD + 16 * r + 2 * t + 1] = acc[t][2];
+      }
+      if (2 * c + 1 < G) {
+        so[(2 * c + 1) * kAttnD + 16 * r + 2 * t] = acc[t][1];
+        so[(2 * c + 1) * kAttnD + 16 * r + 2 * t + 1] = acc[t][3];
+      }
     }
-    s_o[warp][g][lane] = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
   }
   __syncthreads();
   // thread t merges (head g = t / 32 ... ) : G * 32 items, 128 threads
@@ -231,24 +323,39 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const T*
   const float* all = part + (size_t(b) * hkv + h) * nsplit * part_stride;
   for (int item = threadIdx.x; item < G * 32; item += kAttnThreads) {
     const int g = item >> 5, ln = item & 31;
-    float mm = -INFINITY;
-    for (int s2 = 0; s2 < nsplit; ++s2) mm = fmaxf(mm, __ldcg(all + s2 * part_stride + size_t(g) * (4 + kAttnD)));
-    float ll = 0.f;
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    for (int s2 = 0; s2 < nsplit; ++s2) {
-      const float* src = all + s2 * part_stride + size_t(g) * (4 + kAttnD);
-      const float ms = __ldcg(src);
-      const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-      ll += __ldcg(src + 1) * c;
-      a0 += __ldcg(src + 4 + ln * 4 + 0) * c;
-      a1 += __ldcg(src + 4 + ln * 4 + 1) * c;
-      a2 += __ldcg(src + 4 + ln * 4 + 2) * c;
-      a3 += __ldcg(src + 4 + ln * 4 + 3) * c;
+    // eight splits per round: all their loads are in flight together (one L2 round trip per round)
+    float mm = -INFINITY, ll = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+      float2 ml[8];
+      float4 ov[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = s0 + j < nsplit;
+        const float* src = all + size_t(in ? s0 + j : s0) * part_stride + size_t(g) * (4 + kAttnD);
+        ml[j] = __ldcg(reinterpret_cast<const float2*>(src));
+        ov[j] = __ldcg(reinterpret_cast<const float4*>(src + 4 + ln * 4));
+        if (!in) ml[j].x = -INFINITY;
+      }
+      float mnew = mm;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mnew = fmaxf(mnew, ml[j].x);
+      if (mnew == -INFINITY) continue;
+      const float c0 = exp2f(mm - mnew);  // 0 on the first round (mm = -inf)
+      ll *= c0;
+      acc.x *= c0; acc.y *= c0; acc.z *= c0; acc.w *= c0;
+      mm = mnew;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float cj = ml[j].x == -INFINITY ? 0.f : exp2f(ml[j].x - mm);
+        ll += ml[j].y * cj;
+        acc.x += ov[j].x * cj; acc.y += ov[j].y * cj; acc.z += ov[j].z * cj; acc.w += ov[j].w * cj;
+      }
     }
     const float inv = 1.f / ll;
     T* dst = out + size_t(b) * hq * kAttnD + (size_t(h) * G + g) * kAttnD + ln * 4;
-    *reinterpret_cast<T2*>(dst) = Num<T>::down(a0 * inv, a1 * inv);
-    *reinterpret_cast<T2*>(dst + 2) = Num<T>::down(a2 * inv, a3 * inv);
+    *reinterpret_cast<T2*>(dst) = Num<T>::down(acc.x * inv, acc.y * inv);
+    *reinterpret_cast<T2*>(dst + 2) = Num<T>::down(acc.z * inv, acc.w * inv);
   }
   if (threadIdx.x == 0) counters[b * hkv + h] = 0;  // ready for the next launch
 }
@@ -257,8 +364,10 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attention_kernel(const T*
 // act[b, f] = silu(gu[b, f]) * gu[b, F + f]
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, int64_t rows, int F) {
+__global__ void silu_mul_kernel(const T* gu, T* act, int64_t rows, int F) {
   using T2 = typename Num<T>::T2;
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t vec_per_row = F / 8;
   const int64_t total = rows * vec_per_row;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
@@ -284,10 +393,11 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ act, i
 // registers between the statistic and the scaling (rows of up to 8 x 4 x 256 elements, else a second read).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ residual,
-                                                           const T* __restrict__ gamma, T* __restrict__ out, T* __restrict__ res_out,
-                                                           int hidden, float eps) {
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const T* x, const T* residual, const T* __restrict__ gamma, T* out,
+                                                           T* res_out, int hidden, float eps) {
   using T2 = typename Num<T>::T2;
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int U = 4;
   const int64_t row = blockIdx.x;
   const int nvec = hidden / 8;
@@ -353,10 +463,10 @@ template <typename T>
 void launch_attention(int G, dim3 grid, cudaStream_t stream, const T* q, const T* k, const T* v, T* out, float* part,
                       unsigned int* counters, int hq, int hkv, int max_ctx, int ctx, int q_row_stride, float scale_log2) {
   switch (G) {
-    case 1: decode_attention_kernel<T, 1><<<grid, kAttnThreads, 0, stream>>>(q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
-    case 2: decode_attention_kernel<T, 2><<<grid, kAttnThreads, 0, stream>>>(q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
-    case 4: decode_attention_kernel<T, 4><<<grid, kAttnThreads, 0, stream>>>(q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
-    case 8: decode_attention_kernel<T, 8><<<grid, kAttnThreads, 0, stream>>>(q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
+    case 1: launch_pdl(decode_attention_kernel<T, 1>, grid, dim3(kAttnThreads), stream, q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
+    case 2: launch_pdl(decode_attention_kernel<T, 2>, grid, dim3(kAttnThreads), stream, q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
+    case 4: launch_pdl(decode_attention_kernel<T, 4>, grid, dim3(kAttnThreads), stream, q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
+    case 8: launch_pdl(decode_attention_kernel<T, 8>, grid, dim3(kAttnThreads), stream, q, k, v, out, part, counters, hq, hkv, max_ctx, ctx, q_row_stride, scale_log2); break;
     default: B200_REQUIRE(false, "decode attention supports 1, 2, 4 or 8 query heads per KV head, got " << G);
   }
 }
@@ -370,13 +480,11 @@ void rope_kv_append(DType t, void* qkv, void* kcache, void* vcache, int batch, i
   const int threads = head_dim / 2 < 32 ? 32 : head_dim / 2;
   const float l2 = log2f(theta);
   if (t == DType::F16)
-    rope_kv_append_kernel<__half><<<grid, threads, 0, stream>>>(static_cast<__half*>(qkv), static_cast<__half*>(kcache),
-                                                                static_cast<__half*>(vcache), hq, hkv, head_dim, max_ctx, pos, l2);
+    launch_pdl(rope_kv_append_kernel<__half>, grid, dim3(unsigned(threads)), stream, static_cast<__half*>(qkv),
+               static_cast<__half*>(kcache), static_cast<__half*>(vcache), hq, hkv, head_dim, max_ctx, pos, l2);
   else
-    rope_kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(static_cast<__nv_bfloat16*>(qkv),
-                                                                       static_cast<__nv_bfloat16*>(kcache),
-                                                                       static_cast<__nv_bfloat16*>(vcache), hq, hkv, head_dim, max_ctx,
-                                                                       pos, l2);
+    launch_pdl(rope_kv_append_kernel<__nv_bfloat16>, grid, dim3(unsigned(threads)), stream, static_cast<__nv_bfloat16*>(qkv),
+               static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), hq, hkv, head_dim, max_ctx, pos, l2);
   B200_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -386,8 +494,8 @@ size_t decode_attention_workspace_bytes(int batch, int hq, int hkv, int splits) 
 }
 
 int decode_attention_splits(int batch, int hkv, int ctx, int sm_count) {
-  // enough CTAs to fill the GPU twice over, at least 64 positions per split
-  int s = (2 * sm_count + batch * hkv - 1) / (batch * hkv);
+  // two CTAs fit on an SM: as many splits as keep the whole grid resident at once, at least 64 positions each
+  int s = (2 * sm_count) / (batch * hkv);
   const int by_len = (ctx + 63) / 64;
   if (s > by_len) s = by_len;
   if (s < 1) s = 1;
@@ -421,13 +529,13 @@ void add_rmsnorm(DType t, const void* x, const void* residual, const void* gamma
                  float eps, cudaStream_t stream) {
   B200_REQUIRE(hidden % 8 == 0 && rows > 0, "add_rmsnorm: hidden must be a multiple of 8");
   if (t == DType::F16)
-    add_rmsnorm_kernel<__half><<<unsigned(rows), 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(residual),
-                                                                  static_cast<const __half*>(gamma), static_cast<__half*>(out),
-                                                                  static_cast<__half*>(res_out), hidden, eps);
+    launch_pdl(add_rmsnorm_kernel<__half>, dim3(unsigned(rows)), dim3(256), stream, static_cast<const __half*>(x),
+               static_cast<const __half*>(residual), static_cast<const __half*>(gamma), static_cast<__half*>(out),
+               static_cast<__half*>(res_out), hidden, eps);
   else
-    add_rmsnorm_kernel<__nv_bfloat16><<<unsigned(rows), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(gamma),
-        static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(res_out), hidden, eps);
+    launch_pdl(add_rmsnorm_kernel<__nv_bfloat16>, dim3(unsigned(rows)), dim3(256), stream, static_cast<const __nv_bfloat16*>(x),
+               static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(gamma),
+               static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(res_out), hidden, eps);
   B200_CUDA_CHECK(cudaGetLastError());
 }
 
@@ -439,10 +547,11 @@ void silu_mul(DType t, const void* gate_up, void* act, int64_t rows, int ffn, in
   if (blocks > int64_t(sm_count) * 8) blocks = int64_t(sm_count) * 8;
   if (blocks < 1) blocks = 1;
   if (t == DType::F16)
-    silu_mul_kernel<__half><<<unsigned(blocks), threads, 0, stream>>>(static_cast<const __half*>(gate_up), static_cast<__half*>(act), rows, ffn);
+    launch_pdl(silu_mul_kernel<__half>, dim3(unsigned(blocks)), dim3(unsigned(threads)), stream, static_cast<const __half*>(gate_up),
+               static_cast<__half*>(act), rows, ffn);
   else
-    silu_mul_kernel<__nv_bfloat16><<<unsigned(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up),
-                                                                            static_cast<__nv_bfloat16*>(act), rows, ffn);
+    launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(unsigned(blocks)), dim3(unsigned(threads)), stream,
+               static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(act), rows, ffn);
   B200_CUDA_CHECK(cudaGetLastError());
 }
 

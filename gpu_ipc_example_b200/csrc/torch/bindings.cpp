@@ -272,7 +272,7 @@ std::vector<int64_t> fused_ar_scale_cast(std::vector<at::Tensor> ins, std::vecto
 std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::Tensor> ws, std::vector<at::Tensor> residuals,
                                    std::vector<at::Tensor> gammas, std::vector<at::Tensor> outs,
                                    std::vector<at::Tensor> res_outs, std::vector<at::Tensor> workspaces, double eps,
-                                   bool with_norm, int64_t comm_id, int64_t ctas) {
+                                   bool with_norm, int64_t comm_id, int64_t ctas, bool local_only) {
   Comm& c = get(comm_id);
   check_tensors(c, xs, "x");
   check_tensors(c, ws, "weight");
@@ -310,7 +310,7 @@ std::vector<int64_t> fused_gemm_ar(std::vector<at::Tensor> xs, std::vector<at::T
   }
   c10::cuda::CUDAGuard guard(c.device());
   CollInfo info = fused_gemm_allreduce(c, dtype_of(xs[0]), p.data(), M, N, K, float(eps), with_norm, int(ctas),
-                                       at::cuda::getCurrentCUDAStream(c.device()));
+                                       at::cuda::getCurrentCUDAStream(c.device()), local_only);
   return info_vec(info);
 }
 
@@ -413,7 +413,7 @@ TORCH_LIBRARY(b200ipc, m) {
   m.def("fused_ag_gemm(Tensor[] xs, Tensor[] ws, Tensor[] outs, Tensor[] workspaces, int comm, int ctas) -> int[]", &fused_ag_gemm);
   m.def(
       "fused_gemm_ar(Tensor[] xs, Tensor[] ws, Tensor[] residuals, Tensor[] gammas, Tensor[] outs, Tensor[] res_outs, "
-      "Tensor[] workspaces, float eps, bool with_norm, int comm, int ctas) -> int[]",
+      "Tensor[] workspaces, float eps, bool with_norm, int comm, int ctas, bool local_only) -> int[]",
       &fused_gemm_ar);
   m.def("all_reduce(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_reduce);
   m.def("all_gather(Tensor[] ins, Tensor[] outs, int comm, str algo, int ctas, int warps, int flags) -> int[]", &all_gather);

@@ -77,9 +77,13 @@ def apply_rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor
 
 class LlamaTP:
     def __init__(self, cfg: LlamaConfig, comm, batch: int, max_ctx: int, fusion: str = "allreduce", seed: int = 0,
-                 device: Optional[torch.device] = None, kernels: Optional[bool] = None, pack_weights: bool = False):
+                 device: Optional[torch.device] = None, kernels: Optional[bool] = None, pack_weights: bool = False,
+                 local_gemm: Optional[bool] = None):
         assert fusion in ("gemm", "allreduce", "nccl")
         self.cfg, self.comm, self.fusion = cfg, comm, fusion
+        # QKV and gate/up projections on the library's weight-streaming kernel instead of the framework's matmul
+        # (off by default: measured level with cuBLAS at these shapes, a little behind it once the step is a graph)
+        self.local_gemm = bool(local_gemm) and comm is not None
         # the decode kernels are written for head_dim 128 and 1/2/4/8 query heads per KV head
         can = cfg.head_dim == 128 and (cfg.n_heads // cfg.n_kv_heads) in (1, 2, 4, 8) and cfg.ffn % 8 == 0
         self.kernels = can if kernels is None else (kernels and can)
@@ -177,6 +181,15 @@ class LlamaTP:
 
         return cm()
 
+    def _linear(self, xs, ws):
+        """Column-parallel projection of every local rank: the library's weight-streaming kernel when `local_gemm`
+        is on and the shape fits it, else the framework's matmul."""
+        if self.local_gemm and xs[0].shape[0] <= 32 and ws[0].shape[0] % 128 == 0:
+            if self.nlocal == 1 and not self.comm._virtual:
+                return [self.comm.linear(xs[0], ws[0])]
+            return self.comm.linear(list(xs), list(ws))
+        return [x @ w.t() for x, w in zip(xs, ws)]
+
     # ------------------------------------------------------------------ one decode step
     @torch.no_grad()
     def decode(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -189,9 +202,10 @@ class LlamaTP:
         normed = [rms_norm(h[i], self.norm_attn[0], cfg.eps) for i in range(self.nlocal)]
         for l in range(cfg.layers):
             attn_out = []
+            with self._stage("qkv_gemm"):
+                qkv_all = self._linear(normed, [self.wqkv[i][l] for i in range(self.nlocal)])
             for i in range(self.nlocal):
-                with self._stage("qkv_gemm"):
-                    qkv = normed[i] @ self.wqkv[i][l].t()
+                qkv = qkv_all[i]
                 if self.kernels:
                     with self._stage("rope_append"):
                         torch.ops.b200ipc.rope_kv_append(qkv, self.kcache[i][l], self.vcache[i][l], self.hq, self.hkv, pos, cfg.rope_theta)
@@ -211,9 +225,10 @@ class LlamaTP:
             with self._stage("o_proj_allreduce_norm"):
                 normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo_run[i][l] for i in range(self.nlocal)])
             act = []
+            with self._stage("gate_up_gemm"):
+                gu_all = self._linear(normed, [self.wgu[i][l] for i in range(self.nlocal)])
             for i in range(self.nlocal):
-                with self._stage("gate_up_gemm"):
-                    gu = normed[i] @ self.wgu[i][l].t()
+                gu = gu_all[i]
                 if self.kernels:
                     with self._stage("silu_mul"):
                         act.append(torch.ops.b200ipc.silu_mul(gu))

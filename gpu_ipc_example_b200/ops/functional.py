@@ -40,9 +40,12 @@ def shutdown() -> None:
         _default = None
 
 
-def all_reduce(tensor: torch.Tensor, algo: str = "auto", comm: Optional[Communicator] = None) -> torch.Tensor:
-    """In-place sum over ranks (like `dist.all_reduce`)."""
+def all_reduce(tensor, algo: str = "auto", comm: Optional[Communicator] = None):
+    """In-place sum over ranks (like `dist.all_reduce`).  On an emulated world (all ranks on one GPU) every
+    function of this module takes one tensor per rank, as a list."""
     c = comm or default_communicator()
+    if isinstance(tensor, (list, tuple)):
+        return c.all_reduce(list(tensor), None, algo)
     if tensor.is_contiguous() and tensor.data_ptr() % 16 == 0 and c.nlocal == 1:
         return c.all_reduce_(tensor, algo)
     return c.all_reduce(tensor, None, algo)
@@ -54,9 +57,10 @@ def all_gather_into_tensor(output: torch.Tensor, tensor: torch.Tensor, algo: str
     return c.all_gather(tensor, output, algo)
 
 
-def reduce_scatter_tensor(output: torch.Tensor, tensor: torch.Tensor, comm: Optional[Communicator] = None) -> torch.Tensor:
+def reduce_scatter_tensor(output: torch.Tensor, tensor: torch.Tensor, algo: str = "auto",
+                          comm: Optional[Communicator] = None) -> torch.Tensor:
     c = comm or default_communicator()
-    return c.reduce_scatter(tensor, output)
+    return c.reduce_scatter(tensor, output, algo)
 
 
 def allreduce_residual_rmsnorm(x, residual, gamma, eps: float = 1e-5, comm: Optional[Communicator] = None):

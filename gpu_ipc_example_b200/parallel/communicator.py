@@ -277,10 +277,38 @@ class Communicator:
         with_norm = gamma is not None
         want_res = residual is not None
         v = torch.ops.b200ipc.fused_gemm_ar(xs, ws, self._lists(residual) if want_res else [], self._lists(gamma) if with_norm else [],
-                                            L(out), L(res_out) if want_res else [], L(wsp), eps, with_norm, self._h, ctas)
+                                            L(out), L(res_out) if want_res else [], L(wsp), eps, with_norm, self._h, ctas, False)
         self.last_info = CollInfo.from_vec(v)
         if with_norm or want_res:
             return out, res_out
+        return out
+
+    def linear(self, x: TensorOrList, weight: TensorOrList, *, ctas: int = 0):
+        """`x @ weight.T` with no exchange: the column-parallel projections of a decode step (QKV, gate/up) on the
+        same weight-streaming tcgen05 kernel that `linear_allreduce` uses for up to 32 rows (swapped operands,
+        split K, all SMs pulling on the weight).  x: [M <= 32, K], weight: [N, K] with N a multiple of 128, or
+        packed by `pack_weight`; anything else goes to the framework's matmul.  The output lives in the symmetric
+        heap and is reused by the next call with the same shape."""
+        xs = [t.contiguous() for t in self._lists(x)]
+        ws = [t.contiguous() for t in self._lists(weight)]
+        M, N = xs[0].shape[0], ws[0].shape[0] * (64 if ws[0].dim() == 4 else 1)
+        if M > 32 or N % 128 != 0 or xs[0].shape[1] % 8 != 0:
+            if ws[0].dim() == 4:
+                raise ValueError("a packed weight needs M <= 32 rows and N a multiple of 128")
+            return self._ret(x, [a @ w.t() for a, w in zip(xs, ws)])
+        key = ("local", M, N, xs[0].dtype)
+        cache = self.__dict__.setdefault("_gemm_buffers", {})
+        if key not in cache:
+            nbytes = self._C.gemm_ar_workspace_bytes(self.world, M, N)
+            wsp = self.empty([nbytes // 2], torch.float16)
+            for t in (wsp if self._virtual else [wsp]):
+                t.zero_()
+            torch.cuda.synchronize()
+            cache[key] = (wsp, self.empty([M, N], xs[0].dtype))
+        wsp, out = cache[key]
+        L = (lambda t: t) if self._virtual else (lambda t: [t])
+        v = torch.ops.b200ipc.fused_gemm_ar(xs, ws, [], [], L(out), [], L(wsp), 0.0, False, self._h, ctas, True)
+        self.last_info = CollInfo.from_vec(v)
         return out
 
     def allgather_linear(self, x_shard: TensorOrList, weight: TensorOrList, *, ctas: int = 0):
@@ -353,8 +381,8 @@ class Communicator:
         in a multi-process world).  The cached workspaces of the fused GEMM kernels are cleared too, so that
         no flag left by an interrupted launch can be taken for a later one."""
         self._C.reset(self._h)
-        for wsp, _, _ in self.__dict__.get("_gemm_buffers", {}).values():
-            for t in (wsp if self._virtual else [wsp]):
+        for entry in self.__dict__.get("_gemm_buffers", {}).values():
+            for t in (entry[0] if self._virtual else [entry[0]]):
                 t.zero_()
         torch.cuda.synchronize()
         self.barrier()

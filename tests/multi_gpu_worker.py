@@ -93,8 +93,21 @@ def mode_collectives(comm, nvls):
         comm.check()
         shard = n // world
         torch.testing.assert_close(out.float(), want[rank * shard:(rank + 1) * shard], atol=2e-2, rtol=4e-3)
-    # fused all-reduce + residual + RMSNorm at decode shapes
-    for rows, hidden in ((1, 8192), (32, 8192), (16, 3584)):
+    # flag-in-data reduce-scatter: launches back to back (they alternate between the halves of the ring)
+    for algo in ("parallel:ll512", "parallel:ll16", "parallel:ll128", "auto"):
+        cases = []
+        for it in range(40):
+            n = world * (8 if it % 3 == 0 else (4096 if it % 3 == 1 else 2 * 777))
+            x = torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1000 * it + rank)).half()
+            cases.append((x, comm.reduce_scatter(x, None, algo)))
+        torch.cuda.synchronize()
+        comm.check()
+        for x, out in cases[-6:]:
+            want = torch.stack([p.float() for p in gather_inputs(x)]).sum(0)
+            shard = x.numel() // world
+            torch.testing.assert_close(out.float(), want[rank * shard:(rank + 1) * shard], atol=2e-2, rtol=4e-3)
+    # fused all-reduce + residual + RMSNorm at decode shapes, and at a prefill shape (all-reduce + one local kernel)
+    for rows, hidden in ((1, 8192), (32, 8192), (16, 3584), (512, 4096)):
         x = torch.randn(rows, hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(50 + rank)).half()
         res = torch.randn(rows, hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7)).half()
         gam = torch.rand(hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(8)).half() + 0.5
@@ -160,6 +173,16 @@ def mode_linear(comm):
         check_linear(comm, M, K, N, norm=False)
     for it in range(20):
         check_linear(comm, 32, 256, 512, norm=True)
+    # the same kernel without an exchange (column-parallel projections of a decode step)
+    g = torch.Generator(device="cuda").manual_seed(5 + dist.get_rank())
+    for (M, K, N) in ((32, 1024, 1280), (5, 448, 256)):
+        for _ in range(3):
+            x = torch.randn(M, K, device="cuda", generator=g).half()
+            w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).half()
+            y = comm.linear(x, w)
+            torch.cuda.synchronize()
+            comm.check()
+            torch.testing.assert_close(y.float(), x.float() @ w.float().t(), atol=3e-2, rtol=2e-2)
 
 
 @soft

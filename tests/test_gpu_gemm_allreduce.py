@@ -37,6 +37,29 @@ def test_gemm_allreduce_plain(world):
                 torch.testing.assert_close(o.float(), want, atol=3e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_local_linear_on_the_weight_streaming_kernel(world):
+    """`Communicator.linear`: the decode-sized kernel as a plain GEMM (no exchange); every emulated rank gets
+    its own product.  Called twice per shape: the fp32 scratch must be left clean for the next launch."""
+    with Communicator.virtual(world, 0, staging_bytes=96 << 20) as comm:
+        for dtype in (torch.float16, torch.bfloat16):
+            for (M, K, N) in ((1, 512, 256), (32, 1024, 1280), (7, 448, 128), (16, 8192, 1024)):
+                for rep in range(2):
+                    xs, ws, _, _ = _mk(world, M, K, N, dtype, seed=M + rep)
+                    outs = comm.linear(xs, ws)
+                    torch.cuda.synchronize()
+                    comm.check()
+                    assert comm.last_info.launches == 1
+                    for x, w, o in zip(xs, ws, outs):
+                        torch.testing.assert_close(o.float(), x.float() @ w.float().t(), atol=3e-2 if dtype == torch.float16 else 1.5e-1,
+                                                   rtol=2e-2)
+        # shapes the kernel does not take go to the framework's matmul
+        xs, ws, _, _ = _mk(world, 40, 256, 192, torch.float16)
+        outs = comm.linear(xs, ws)
+        for x, w, o in zip(xs, ws, outs):
+            torch.testing.assert_close(o.float(), x.float() @ w.float().t(), atol=3e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("world", [1, 8])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_gemm_allreduce_residual_rmsnorm(world, dtype):

@@ -187,8 +187,8 @@ def test_reduce_scatter_refuses_what_one_pass_cannot_hold(comm):
     xs = [torch.zeros(n, dtype=torch.float16, device="cuda") for _ in range(comm.world)]
     with pytest.raises(RuntimeError, match="more than the"):
         comm.reduce_scatter(xs, None, "parallel:ll8")
-    xs = [x[:n // 2] for x in xs]
-    outs = comm.reduce_scatter(xs, None, "auto")  # above 2 MiB auto takes the barrier-based kernel
+    xs = [torch.zeros(6 << 20, dtype=torch.float16, device="cuda") for _ in range(comm.world)]  # 12 MiB
+    outs = comm.reduce_scatter(xs, None, "auto")  # above 8 MiB auto takes the barrier-based kernel
     torch.cuda.synchronize()
     comm.check()
     assert comm.last_info.sched in ("bulk", "nvls") and float(outs[0].abs().max()) == 0.0
