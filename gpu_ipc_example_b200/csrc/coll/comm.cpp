@@ -573,6 +573,13 @@ CollInfo Comm::launch_bulk(BulkModeId mode, bool nvls, DType t, const void* cons
   const int64_t ntiles = std::max<int64_t>(1, cdiv(shard_vec, tile_vec));
   const int64_t rounds = cdiv(ntiles, cap);
   int ctas = geom.ctas > 0 ? geom.ctas : int(cdiv(ntiles, rounds));
+  if (geom.ctas <= 0 && nvls && mode == BulkModeId::AllReduce) {
+    // The in-switch reduction is fed by few CTAs: every CTA runs its own cross-rank barrier pair, and a handful
+    // of CTAs already keeps the links busy (16 MiB on 8 GPUs: 47.7 us with 8 CTAs, 58.3 us with 64).
+    int want = nvls_ctas_for(nelems * 2);
+    if (const char* e = std::getenv("B200IPC_NVLS_CTAS")) want = std::atoi(e);
+    if (want > 0) ctas = int(std::min<int64_t>(std::min<int64_t>(want, cap), ntiles));
+  }
   B200_REQUIRE(ctas <= cap, "requested " << ctas << " CTAs but only " << cap << " can be resident");
 
   KArgs args;
@@ -683,12 +690,17 @@ CollInfo Comm::all_gather(AlgoSpec algo, DType t, const void* const* ins, void* 
     const size_t bytes = nelems * 2;
     // two ranks: the direct flag-in-data push moves the same bytes as any other form and needs no
     // barrier; measured ahead of the barrier-based kernels and of NCCL up to 64 MiB per rank
-    if (world_ == 2 || bytes <= (size_t(1) << 20) / size_t(world_) || nelems % 8 != 0) {
+    // measured on 8 GPUs (bytes per rank): the direct push wins up to 1 MiB (23 us against NCCL's 47), the
+    // barrier kernel with peer loads from 2 to 8 MiB, the flag-in-data ring above (level with NCCL)
+    if (world_ == 2 || bytes <= (size_t(1) << 20) || nelems % 8 != 0) {
       algo.sched = SchedKind::Ring;
       algo.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
       algo.direct_allgather = true;
+    } else if (bytes <= (size_t(8) << 20)) {
+      algo.sched = SchedKind::Bulk;
     } else {
-      algo.sched = has_nvls() ? SchedKind::Nvls : SchedKind::Bulk;
+      algo.sched = SchedKind::Ring;
+      algo.proto = safe_protos_ ? ProtoKind::LL16 : ProtoKind::LL512;
     }
   }
   if (algo.sched == SchedKind::Bulk || algo.sched == SchedKind::Nvls)

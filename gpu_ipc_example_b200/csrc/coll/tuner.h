@@ -28,15 +28,11 @@ constexpr size_t KiB = 1024, MiB = 1024 * 1024;
 
 // `large` is filled in by the caller: Nvls or Bulk depending on what the world supports.
 inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
+  // 8 ranks, three rows each (the dynamic programme of tune.py over the device-timed sweep of every schedule)
   static const TuneRow w8_sym[] = {
-      {128 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {2 * MiB, SchedKind::Bisect, ProtoKind::LL512},      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},
-      {8 * MiB, SchedKind::Ring, ProtoKind::LL512},        {0, SchedKind::Nvls, ProtoKind::LL512}};
+      {64 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {1 * MiB, SchedKind::Parallel, ProtoKind::LL512}, {0, SchedKind::Nvls, ProtoKind::LL512}};
   static const TuneRow w8_user[] = {
-      {128 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {2 * MiB, SchedKind::Bisect, ProtoKind::LL512},      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},
-      {8 * MiB, SchedKind::Ring, ProtoKind::LL512},        {32 * MiB, SchedKind::Sequential, ProtoKind::LL512},
-      {0, SchedKind::Nvls, ProtoKind::LL512}};
+      {64 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {64 * MiB, SchedKind::Parallel, ProtoKind::LL512}, {0, SchedKind::Ring, ProtoKind::LL512}};
   static const TuneRow w4_sym[] = {
       {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
       {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {8 * MiB, SchedKind::Parallel, ProtoKind::LL512},
@@ -54,7 +50,7 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
   static const TuneRow w2_user[] = {
       {4 * MiB, SchedKind::OneShot, ProtoKind::LL512},     {0, SchedKind::Ring, ProtoKind::LL512}};
   if (world >= 8) {
-    *rows = symmetric ? 6 : 7;
+    *rows = 3;
     return symmetric ? w8_sym : w8_user;
   }
   if (world >= 4) {
@@ -63,6 +59,16 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
   }
   *rows = symmetric ? 3 : 2;
   return symmetric ? w2_sym : w2_user;
+}
+
+// CTAs of the in-switch (NVLS) all-reduce for a message of `bytes` (8 ranks, symmetric buffers): few while the
+// two barrier rounds dominate, more as the data does.
+inline int nvls_ctas_for(size_t bytes) {
+  const size_t per_cta = 2 * MiB;
+  size_t c = bytes / per_cta;
+  if (c < 8) c = 8;
+  if (c > 256) c = 256;
+  return int(c);
 }
 
 }  // namespace b200ipc

@@ -96,7 +96,8 @@ GemmArWorkspace gemm_ar_workspace(int world, int64_t M, int64_t N) {
   const size_t rs_flags = size_t(world) * size_t(m_tiles) * size_t(N / 64) * 4 * sizeof(uint32_t);
   const size_t os_flags = size_t(N / 64) * 4 * kDecodeMaxSplits * sizeof(uint32_t);
   w.flags_bytes = up256(std::max(rs_flags, os_flags));
-  w.inv_bytes = up256(size_t(M) * sizeof(float));
+  // [M] fp32 (reduce-scatter form), or [M][8] 8-byte words: the row-statistic hand-over of the decode-sized form
+  w.inv_bytes = up256(std::max(size_t(M) * sizeof(float), size_t(std::min<int64_t>(M, 32)) * 8 * sizeof(uint64_t)));
   return w;
 }
 
@@ -169,6 +170,11 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
   args.eps = eps;
   args.with_norm = with_norm ? 1 : 0;
   args.local_only = local_only ? 1 : 0;
+  // few rows, many CTAs: several CTAs share a row in the exchange, so that its transactions leave from many SMs
+  int parts = 1;
+  if (with_norm && std::getenv("B200IPC_GEMM_ROW_PARTS_OFF") == nullptr)
+    while (parts < 8 && M * parts * 2 <= ctas && (N / 2) % (parts * 2 * 4) == 0) parts *= 2;
+  args.row_parts = parts;
   args.landing_off = landing_off;
   args.flags_off = landing_off + ws.landing_bytes;
   args.inv_off = args.flags_off + ws.flags_bytes;

@@ -73,6 +73,7 @@ struct GemmArArgs {
   float eps;
   int with_norm;         // 0: out = sum (+ residual if given); 1: RMSNorm as well
   int local_only;        // 1: no exchange at all, out = this rank's own product (decode-sized kernel only)
+  int row_parts;         // decode-sized kernel with RMSNorm: CTAs that share one row in the exchange (1, 2, 4 or 8)
   // heap offsets (same on every rank)
   uint64_t landing_off;  // reduce-scatter: [world][rows_per_rank][N] partials from every source; one-shot: [M][N], this rank's own
   uint64_t flags_off;    // reduce-scatter: [world][m_tiles][n_tiles][4]; one-shot: [n_tiles]   uint32

@@ -293,6 +293,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_decode_kernel(const __gr
       op.nelems = uint64_t(M) * uint64_t(N);
       op.hidden = N;
       op.scale_or_eps = args.with_norm ? args.eps : 1.0f;
+      op.trace = reinterpret_cast<unsigned long long*>(me.heap + lay.ctrl_off + kGemmTraceOff) + 11;
+      op.row_parts = args.with_norm ? args.row_parts : 1;
+      op.stat_scratch = reinterpret_cast<unsigned long long*>(me.heap + args.inv_off);
+      op.stat_epoch = epoch;
       float* part = s.exchange_part;
       int* ab = &s.exchange_abort;
       if (args.with_norm) {

@@ -37,6 +37,14 @@ struct FusedOperands {
   uint64_t nelems;       // rows * hidden
   int hidden;            // row length (kEpiNorm)
   float scale_or_eps;    // kEpiScale: multiplier; kEpiNorm: epsilon
+  unsigned long long* trace = nullptr;  // optional: 5 time stamps of CTA 0 (entry, set-up, sent, summed, statistic)
+  // kEpiNorm, optional: a row is shared by `row_parts` CTAs (CTA b takes part b % row_parts of row b / row_parts),
+  // so that a handful of rows still spreads its exchange over many SMs.  The CTAs of a row combine their sums of
+  // squares through `stat_scratch`: [rows][row_parts] 8-byte words {stat_epoch, partial sum}, written whole, so
+  // the epoch doubles as the flag.  stat_epoch must differ from launch to launch on the same scratch.
+  int row_parts = 1;
+  unsigned long long* stat_scratch = nullptr;
+  uint32_t stat_epoch = 0;
 };
 
 // The whole exchange + epilogue for the calling CTA (all its threads call it).  Written as a function
@@ -55,6 +63,10 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   const int warp = int(threadIdx.x >> 5);
   const int warps = int(blockDim.x >> 5);
   const int wire = int(blockIdx.x) * warps + warp;
+  auto stamp = [&](int i) {
+    if (op.trace && blockIdx.x == 0 && threadIdx.x == 0) op.trace[i] = globaltimer_ns();
+  };
+  stamp(0);
 
   uint32_t seq = me.seq;
   if (me.seq_dev) seq += ld_volatile_u32(me.seq_dev);
@@ -71,7 +83,21 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   int64_t d0, d1;
   int row0 = 0, nrows = 0;
   int64_t row_dw = 0;
-  if (EPI == kEpiNorm) {
+  const int parts = (EPI == kEpiNorm && op.row_parts > 1) ? op.row_parts : 1;
+  if (EPI == kEpiNorm && parts > 1) {
+    row_dw = op.hidden / 2;
+    const int rows = int(total_dw / row_dw);
+    const int64_t seg_dw = row_dw / parts;
+    const int seg = int(blockIdx.x);
+    if (seg < rows * parts) {
+      row0 = seg / parts;
+      nrows = 1;
+      d0 = int64_t(row0) * row_dw + int64_t(seg % parts) * seg_dw;
+      d1 = d0 + seg_dw;
+    } else {
+      d0 = d1 = 0;
+    }
+  } else if (EPI == kEpiNorm) {
     row_dw = op.hidden / 2;
     const int rows = int(total_dw / row_dw);
     const int per = (rows + int(gridDim.x) - 1) / int(gridDim.x);
@@ -153,6 +179,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
   constexpr int KMAX = 3;
   const bool fast = steps <= KMAX;
   if (fast) {
+    stamp(1);
     typename B::Msg own[KMAX], rsd[KMAX], gam[KMAX];
     RawIn raw[KMAX];
     const bool norm_in_regs = EPI == kEpiNorm && nrows == 1;
@@ -165,7 +192,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
       load_in_issue(own[k], raw[k], dw);
       if (EPI == kEpiNorm) {
         B::load(rsd[k], residual, dw, d1, -1);
-        if (norm_in_regs) B::load(gam[k], static_cast<const uint32_t*>(op.gamma), dw - d0, row_dw, -1);
+        if (norm_in_regs) B::load(gam[k], static_cast<const uint32_t*>(op.gamma), dw - int64_t(row0) * row_dw, row_dw, -1);
       }
     }
 #pragma unroll
@@ -184,6 +211,7 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
       }
       if (EPI == kEpiNorm) B::shuffle(rsd[k]);
     }
+    stamp(2);
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < KMAX; ++k) {
@@ -224,15 +252,67 @@ __device__ __forceinline__ void oneshot_fused_body(const RankView& me, const Hea
       }
     }
     if (!ok) s_abort = 1;
+    stamp(3);
     if (norm_in_regs) {
       // the reduction order depends on nothing but the thread index: every rank computes the same bits
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (lane == 0) s_part[warp] = ss;
       __syncthreads();
+      if (parts > 1 && s_abort == 0) {
+        // this CTA's share of the row statistic goes out as one 8-byte word {epoch, sum}; the sums of all
+        // parts are then added in part order, so every CTA of the row (and every rank) gets the same bits
+        unsigned long long* slots = op.stat_scratch + size_t(row0) * parts;
+        if (threadIdx.x == 0) {
+          float mine = 0.f;
+          for (int w = 0; w < warps; ++w) mine += s_part[w];
+          const unsigned long long word = (static_cast<unsigned long long>(__float_as_uint(mine)) << 32) | op.stat_epoch;
+          asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(slots + (int(blockIdx.x) % parts)), "l"(word) : "memory");
+        }
+        if (int(threadIdx.x) < parts) {
+          uint32_t spins = 0;
+          uint64_t t0 = 0;
+          for (;;) {
+            unsigned long long word;
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(slots + threadIdx.x) : "memory");
+            if (uint32_t(word) == op.stat_epoch) {
+              s_part[16 + threadIdx.x] = __uint_as_float(uint32_t(word >> 32));
+              break;
+            }
+            if ((++spins & 0x3fu) == 0) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (now - t0 > me.timeout_ns || ld_volatile_u32(waiter.abort_word()) != 0) {
+                if (claim_status(waiter.abort_word(), kTimeout)) {
+                  StatusBlock* sb = me.status;
+                  sb->rank = uint32_t(me.rank);
+                  sb->peer = uint32_t(me.rank);
+                  sb->wire = blockIdx.x;
+                  sb->step = threadIdx.x;
+                  sb->expected = op.stat_epoch;
+                  sb->seen = uint32_t(word);
+                  sb->where = 6;  // the row-statistic hand-over between the CTAs of a row
+                  __threadfence_system();
+                  sb->code = kTimeout;
+                  __threadfence_system();
+                }
+                st_volatile_u32(waiter.abort_word(), 1u);
+                s_abort = 1;
+                break;
+              }
+            }
+          }
+        }
+        __syncthreads();
+      }
+      stamp(4);
       if (s_abort == 0) {
         float tot = 0.f;
-        for (int w = 0; w < warps; ++w) tot += s_part[w];
+        if (parts > 1) {
+          for (int q = 0; q < parts; ++q) tot += s_part[16 + q];
+        } else {
+          for (int w = 0; w < warps; ++w) tot += s_part[w];
+        }
         const float inv = rsqrtf(tot / float(op.hidden) + scale);
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) {
