@@ -147,9 +147,9 @@ class LlamaTP:
         if self.fusion == "gemm":
             out, res = self.comm.linear_allreduce(x if self.nlocal > 1 else x[0], w if self.nlocal > 1 else w[0],
                                                   residual if self.nlocal > 1 else residual[0], gam if self.nlocal > 1 else gamma, eps)
-            out, res = (out, res) if isinstance(out, list) else ([out], [res])
-            # the kernel's output buffers are reused by the next call of the same shape: hand out copies
-            return [o.clone() for o in out], [r.clone() for r in res]
+            # the library alternates between two sets of output buffers per shape, so `res` stays valid as the
+            # residual of the next call and `out` until the call after that: no copies
+            return (out, res) if isinstance(out, list) else ([out], [res])
         assert w[0].dim() == 2, "packed weights are for fusion='gemm'"
         parts = [xi @ wi.t() for xi, wi in zip(x, w)]
         if self.fusion == "allreduce":

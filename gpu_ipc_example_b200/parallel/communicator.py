@@ -257,8 +257,9 @@ class Communicator:
         x: [M, K_local], weight: [N, K_local] (nn.Linear layout) of this rank, or that weight packed once by
         `pack_weight` (faster, most of all at decode sizes).  Returns
         `y = all_reduce(x @ weight.T)` when neither residual nor gamma is given, else the pair
-        `(RMSNorm(y + residual) * gamma, y + residual)`.  Outputs live in the symmetric heap and are
-        reused by the next call with the same shape: consume (or copy) them before calling again."""
+        `(RMSNorm(y + residual) * gamma, y + residual)`.  Outputs live in the symmetric heap; calls of one shape
+        alternate between two sets of them, so a result stays valid through the next call of that shape (it may
+        be that call's residual) and is overwritten by the one after."""
         xs = [t.contiguous() for t in self._lists(x)]
         ws = [t.contiguous() for t in self._lists(weight)]
         M, N = xs[0].shape[0], ws[0].shape[0] * (64 if ws[0].dim() == 4 else 1)  # 4-D: packed by pack_weight
@@ -271,8 +272,11 @@ class Communicator:
                 t.zero_()
             torch.cuda.synchronize()
             self.barrier()  # nobody may push into a workspace that its owner is still clearing
-            cache[key] = (wsp, self.empty([M, N], xs[0].dtype), self.empty([M, N], xs[0].dtype))
-        wsp, out, res_out = cache[key]
+            # two sets of outputs, used in turn: the `res_out` of one call can be the `residual` of the next
+            cache[key] = [wsp, [(self.empty([M, N], xs[0].dtype), self.empty([M, N], xs[0].dtype)) for _ in range(2)], 0]
+        entry = cache[key]
+        wsp, (out, res_out) = entry[0], entry[1][entry[2]]
+        entry[2] ^= 1
         L = (lambda t: t) if self._virtual else (lambda t: [t])
         with_norm = gamma is not None
         want_res = residual is not None
@@ -311,8 +315,12 @@ class Communicator:
         self.last_info = CollInfo.from_vec(v)
         return out
 
-    def allgather_linear(self, x_shard: TensorOrList, weight: TensorOrList, *, ctas: int = 0):
+    def allgather_linear(self, x_shard: TensorOrList, weight: TensorOrList, *, ctas: int = 0, fused: Optional[bool] = None):
         """Column-parallel linear layer on row-sharded activations, all-gather fused into the GEMM kernel.
+
+        fused=None picks by size: the fused kernel from 4096 gathered rows up (level with cuBLAS + NCCL at 8192
+        rows on 8 GPUs); below that this library's all-gather followed by the framework's matmul, which measured
+        ahead of both the fused kernel and NCCL + cuBLAS (128 rows: 49 us against 60 and 55).
 
         x_shard: [M / world, K] (this rank's rows), weight: [N_local, K].  Returns `concat(x_shards) @ weight.T`,
         shape [M, N_local]: every rank pushes its rows to all ranks and the tcgen05/TMA GEMM starts on the rows
@@ -320,6 +328,12 @@ class Communicator:
         xs = [t.contiguous() for t in self._lists(x_shard)]
         ws = [t.contiguous() for t in self._lists(weight)]
         M, K, N = xs[0].shape[0] * self.world, xs[0].shape[1], ws[0].shape[0]
+        if fused is None:
+            fused = M >= 4096 or self.world == 1
+        if not fused:
+            gathered = self.all_gather(xs if self._virtual else xs[0], None, "allgather_auto")
+            gs = gathered if self._virtual else [gathered]
+            return self._ret(x_shard, [g.view(M, K) @ w.t() for g, w in zip(gs, ws)])
         cache = self.__dict__.setdefault("_ag_buffers", {})
         key = (M, K)
         if key not in cache:

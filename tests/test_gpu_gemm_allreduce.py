@@ -88,6 +88,26 @@ def test_repeated_calls_reuse_the_workspace():
             torch.testing.assert_close(new_res[3].float(), s, atol=4e-2, rtol=2e-2)
 
 
+def test_result_of_one_call_is_the_residual_of_the_next():
+    """Calls of one shape alternate between two sets of output buffers: a decoder chains them without copies."""
+    with Communicator.virtual(2, 0, staging_bytes=64 << 20) as comm:
+        xs, ws, res, gam = _mk(2, 16, 256, 512, torch.float16, seed=11)
+        _, r1 = comm.linear_allreduce(xs, ws, [res] * 2, [gam] * 2)
+        _, r2 = comm.linear_allreduce(xs, ws, r1, [gam] * 2)
+        out3, r3 = comm.linear_allreduce(xs, ws, r2, [gam] * 2)
+        torch.cuda.synchronize()
+        comm.check()
+        assert r1[0].data_ptr() != r2[0].data_ptr() and r1[0].data_ptr() == r3[0].data_ptr()
+        y = _ref(xs, ws)
+        s1 = (y + res.float()).half().float()
+        s2 = (y + s1).half().float()
+        s3 = (y + s2).half().float()
+        torch.testing.assert_close(r2[1].float(), s2, atol=4e-2, rtol=2e-2)
+        torch.testing.assert_close(r3[0].float(), s3, atol=6e-2, rtol=2e-2)
+        want = s3 * torch.rsqrt(s3.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float()
+        torch.testing.assert_close(out3[0].float(), want, atol=6e-2, rtol=2e-2)
+
+
 def test_graph_replay_with_device_side_counters():
     with Communicator.virtual(4, 0, staging_bytes=64 << 20, device_seq=True) as comm:
         xs, ws, res, gam = _mk(4, 32, 256, 512, torch.float16, seed=3)
