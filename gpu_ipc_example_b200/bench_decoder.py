@@ -35,8 +35,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--no-kernels", action="store_true", help="plain PyTorch ops for RoPE / cache append / attention / SiLU*up")
     ap.add_argument("--pack", action="store_true", help="gemm arm: row-parallel weights packed by Communicator.pack_weight")
-    ap.add_argument("--own-projections", action="store_true",
-                    help="QKV and gate/up through the library's weight-streaming kernel instead of the framework's matmul")
+    ap.add_argument("--own-projections", nargs="?", const="both", default=None, choices=["both", "qkv", "gate_up"],
+                    help="QKV and / or gate/up through the library's weight-streaming kernel instead of the framework's matmul")
     ap.add_argument("--breakdown", action="store_true", help="also time the stages of one eager step with CUDA events")
     ap.add_argument("--per-rank-shapes-of", type=int, default=0,
                     help="single-GPU dry run: use the per-rank shapes of this tensor-parallel degree with a world of one")
@@ -77,7 +77,7 @@ def main():
             comm = Communicator.virtual(1, local, staging_bytes=256 << 20, device_seq=True)
         model = LlamaTP(cfg, comm, batch=args.batch, max_ctx=args.ctx, fusion=arm, seed=3,
                         kernels=False if args.no_kernels else None, pack_weights=args.pack,
-                        local_gemm=args.own_projections)
+                        local_gemm=True if args.own_projections == "both" else args.own_projections)
         model.pos = args.ctx - 1  # attend over a full context (the cache holds zeros: timing only)
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):

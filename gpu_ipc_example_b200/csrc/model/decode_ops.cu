@@ -494,8 +494,11 @@ size_t decode_attention_workspace_bytes(int batch, int hq, int hkv, int splits) 
 }
 
 int decode_attention_splits(int batch, int hkv, int ctx, int sm_count) {
-  // two CTAs fit on an SM: as many splits as keep the whole grid resident at once, at least 64 positions each
+  // two CTAs fit on an SM: as many splits as keep the whole grid resident at once, at least 64 positions each;
+  // a power of two where that is close, so that a power-of-two context divides into whole, equal warp shares
   int s = (2 * sm_count) / (batch * hkv);
+  if (s >= 8 && s < 12) s = 8;
+  else if (s >= 4 && s < 6) s = 4;
   const int by_len = (ctx + 63) / 64;
   if (s > by_len) s = by_len;
   if (s < 1) s = 1;

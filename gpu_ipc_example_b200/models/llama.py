@@ -78,12 +78,13 @@ def apply_rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor
 class LlamaTP:
     def __init__(self, cfg: LlamaConfig, comm, batch: int, max_ctx: int, fusion: str = "allreduce", seed: int = 0,
                  device: Optional[torch.device] = None, kernels: Optional[bool] = None, pack_weights: bool = False,
-                 local_gemm: Optional[bool] = None):
+                 local_gemm=None):
         assert fusion in ("gemm", "allreduce", "nccl")
         self.cfg, self.comm, self.fusion = cfg, comm, fusion
         # QKV and gate/up projections on the library's weight-streaming kernel instead of the framework's matmul
         # (off by default: measured level with cuBLAS at these shapes, a little behind it once the step is a graph)
-        self.local_gemm = bool(local_gemm) and comm is not None
+        # True / False, or "qkv" / "gate_up" for one of the two projections only
+        self.local_gemm = local_gemm if comm is not None else False
         # the decode kernels are written for head_dim 128 and 1/2/4/8 query heads per KV head
         can = cfg.head_dim == 128 and (cfg.n_heads // cfg.n_kv_heads) in (1, 2, 4, 8) and cfg.ffn % 8 == 0
         self.kernels = can if kernels is None else (kernels and can)
@@ -181,10 +182,10 @@ class LlamaTP:
 
         return cm()
 
-    def _linear(self, xs, ws):
+    def _linear(self, xs, ws, which="qkv"):
         """Column-parallel projection of every local rank: the library's weight-streaming kernel when `local_gemm`
         is on and the shape fits it, else the framework's matmul."""
-        if self.local_gemm and xs[0].shape[0] <= 32 and ws[0].shape[0] % 128 == 0:
+        if self.local_gemm in (True, which) and xs[0].shape[0] <= 32 and ws[0].shape[0] % 128 == 0:
             if self.nlocal == 1 and not self.comm._virtual:
                 return [self.comm.linear(xs[0], ws[0])]
             return self.comm.linear(list(xs), list(ws))
@@ -226,7 +227,7 @@ class LlamaTP:
                 normed, h = self._reduce_norm(h, self.norm_mlp[l], attn_out, [self.wo_run[i][l] for i in range(self.nlocal)])
             act = []
             with self._stage("gate_up_gemm"):
-                gu_all = self._linear(normed, [self.wgu[i][l] for i in range(self.nlocal)])
+                gu_all = self._linear(normed, [self.wgu[i][l] for i in range(self.nlocal)], "gate_up")
             for i in range(self.nlocal):
                 gu = gu_all[i]
                 if self.kernels:
