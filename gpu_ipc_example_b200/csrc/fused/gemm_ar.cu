@@ -172,7 +172,7 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
   args.local_only = local_only ? 1 : 0;
   // few rows, many CTAs: several CTAs share a row in the exchange, so that its transactions leave from many SMs
   int parts = 1;
-  if (with_norm && std::getenv("B200IPC_GEMM_ROW_PARTS_OFF") == nullptr)
+  if (with_norm && W > 1 && !local_only && std::getenv("B200IPC_GEMM_ROW_PARTS_OFF") == nullptr)
     while (parts < 8 && M * parts * 2 <= ctas && (N / 2) % (parts * 2 * 4) == 0) parts *= 2;
   args.row_parts = parts;
   args.landing_off = landing_off;
@@ -222,7 +222,11 @@ CollInfo fused_gemm_allreduce(Comm& comm, DType t, const GemmArPtrs* ptrs, int64
     return fused_gemm_decode(comm, t, ptrs, M, N, K, eps, with_norm, ctas_req, stream, false);
   // Tile width: narrow tiles give small-M problems enough CTAs to stream the weight; wide tiles
   // cut the operand traffic per FLOP for large M.
-  const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  if (const char* e = std::getenv("B200IPC_GEMM_BN")) {  // experiments: force the tile width
+    const int v = std::atoi(e);
+    if ((v == 64 || v == 128 || v == 256) && N % v == 0) BN = v;
+  }
   const bool decode = BN == 64 && M <= kDecodeRows;  // short X stage, deep ring
   const void* fn;
   size_t smem;
@@ -372,7 +376,11 @@ CollInfo fused_allgather_gemm(Comm& comm, DType t, const AgGemmPtrs* ptrs, int64
   B200_REQUIRE(M % W == 0, "the rows of X must divide evenly over the ranks");
   B200_REQUIRE(!comm.device_seq(), "the all-gather + GEMM kernel keeps its counters on the host");
   B200_CUDA_CHECK(cudaSetDevice(comm.device()));
-  const int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  int BN = (M <= 128 || N % 128 != 0) ? 64 : ((M >= 512 && N % 256 == 0) ? 256 : 128);
+  if (const char* e = std::getenv("B200IPC_GEMM_BN")) {  // experiments: force the tile width
+    const int v = std::atoi(e);
+    if ((v == 64 || v == 128 || v == 256) && N % v == 0) BN = v;
+  }
   const void* fn;
   size_t smem;
   const bool h = t == DType::F16;

@@ -282,7 +282,7 @@ struct DevBackend : WireFormat<K> {
       ld_volatile_v4(p, v.d);
     }
   }
-  // This lane's verdict on its part of the transaction.
+  // This lane's decision on its part of the transaction.
   __device__ static bool recv_ok(const Msg& v, uint32_t flag) {
     const int l = lane();
     if constexpr (K == ProtoKind::LL8) {
