@@ -39,3 +39,34 @@ def test_allgather_any_size_any_grid(world, op, proto, half_n, nwires):
     want = np.concatenate(ins).view(np.uint16)
     for o in outs:
         assert (o.view(np.uint16) == want).all()
+
+
+@settings(max_examples=40, deadline=None)
+@given(world=st.sampled_from([2, 4, 8]), proto=st.sampled_from(PROTOS), k=st.integers(min_value=1, max_value=1500),
+       groups=st.integers(min_value=1, max_value=4), launches=st.integers(min_value=1, max_value=4))
+def test_reduce_scatter_any_size_any_grid_back_to_back(world, proto, k, groups, launches):
+    """Slices of k dwords per rank, several launches in a row on the same rings (they alternate between the two halves)."""
+    import ctypes
+
+    n = 2 * world * k
+    payload = {"LL8": 32, "LL16": 64, "LL128": 30, "LL512": 120}[proto]
+    while -(-k // (groups * payload)) > 8:  # a launch takes at most 8 steps
+        groups += 1
+    heaps = (ctypes.c_void_p * world)()
+    seq = 0x1000 + k
+    try:
+        for it in range(launches):
+            rng = np.random.default_rng(k + it)
+            ins = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]
+            outs = [np.full(n // world + 2, 5.0, np.float16) for _ in range(world)]
+            rc, st_ = emu.run_threads(world, "reduce_scatter", proto, ins, [o[:n // world] for o in outs], n, world * groups,
+                                      seq=seq, heaps=heaps)
+            assert rc == 0, st_
+            want = np.sum(np.stack([x.astype(np.float32) for x in ins]), 0)
+            c = n // world
+            for r, o in enumerate(outs):
+                np.testing.assert_allclose(o[:c].astype(np.float32), want[r * c:(r + 1) * c], atol=2e-2, rtol=4e-3)
+                assert (o[c:] == 5.0).all(), "wrote past the end of the slice"
+            seq += 2
+    finally:
+        emu.lib().b200emu_free_heaps(world, heaps)
