@@ -33,14 +33,11 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
       {64 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {1 * MiB, SchedKind::Parallel, ProtoKind::LL512}, {0, SchedKind::Nvls, ProtoKind::LL512}};
   static const TuneRow w8_user[] = {
       {64 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {64 * MiB, SchedKind::Parallel, ProtoKind::LL512}, {0, SchedKind::Ring, ProtoKind::LL512}};
+  // 4 ranks, from the 4-GPU sweep: the in-switch kernel (8 CTAs) is ahead of peer loads from 512 KiB up
   static const TuneRow w4_sym[] = {
-      {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {8 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {0, SchedKind::Bulk, ProtoKind::LL512}};
+      {128 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {1 * MiB, SchedKind::Parallel, ProtoKind::LL512}, {0, SchedKind::Nvls, ProtoKind::LL512}};
   static const TuneRow w4_user[] = {
-      {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {1 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {4 * MiB, SchedKind::Sequential, ProtoKind::LL512},  {16 * MiB, SchedKind::Parallel, ProtoKind::LL512},
-      {0, SchedKind::Bulk, ProtoKind::LL512}};
+      {256 * KiB, SchedKind::OneShot, ProtoKind::LL16}, {4 * MiB, SchedKind::Sequential, ProtoKind::LL512}, {0, SchedKind::Parallel, ProtoKind::LL512}};
   // two ranks: one hop moves as many bytes as two, so the one-shot schedule reaches far
   static const TuneRow w2_sym[] = {
       {512 * KiB, SchedKind::OneShot, ProtoKind::LL512},   {2 * MiB, SchedKind::Sequential, ProtoKind::LL512},
@@ -54,7 +51,7 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
     return symmetric ? w8_sym : w8_user;
   }
   if (world >= 4) {
-    *rows = 5;
+    *rows = 3;
     return symmetric ? w4_sym : w4_user;
   }
   *rows = symmetric ? 3 : 2;
@@ -64,7 +61,8 @@ inline const TuneRow* tune_table(int world, bool symmetric, int* rows) {
 // CTAs of the in-switch (NVLS) all-reduce.  Measured on 8 GPUs with 4, 8, 12, 16, 24, 32 and 148 CTAs from 1 MiB
 // to 512 MiB: 8 CTAs were the fastest at every size (16 MiB: 49.2 us against 59.0 with 32; 512 MiB: 1120 us
 // against 1175 with 148) - the switch's reduction path is saturated by a few hundred loads in flight, and every
-// further CTA adds its own pair of cross-rank barriers.
+// further CTA adds its own pair of cross-rank barriers.  Same on 4 GPUs (8 against 16 CTAs, 2 - 256 MiB).  Only for
+// buffers in the symmetric heap: with staging copies the CTAs also do the copies and many are wanted.
 inline int nvls_ctas_for(size_t /*bytes*/) { return 8; }
 
 }  // namespace b200ipc
