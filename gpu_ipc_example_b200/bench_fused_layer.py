@@ -155,14 +155,14 @@ def main():
         residual = torch.randn(M, N, device="cuda", generator=gres).to(dtype)
 
         def fused(i):
-            return comm.linear_allreduce(x, weights[i % ncopy], residual, gamma, 1e-5)
+            return comm.linear_allreduce(x, weights[i % ncopy], residual, gamma, 1e-5, fused=True)
 
         def two_step(i):
             y = x @ weights[i % ncopy].t()
             return comm.allreduce_residual_rmsnorm(y, residual, gamma, 1e-5)
 
         def fused_g(i):
-            return comm_g.linear_allreduce(x, weights[i % ncopy], residual, gamma, 1e-5)
+            return comm_g.linear_allreduce(x, weights[i % ncopy], residual, gamma, 1e-5, fused=True)
 
         def two_step_g(i):
             y = x @ weights[i % ncopy].t()

@@ -133,7 +133,7 @@ def check_linear(comm, M, K, N, dtype=torch.float16, norm=True):
     part = (x.float() @ w.float().t()).to(dtype)
     total = torch.stack([p.float() for p in gather_inputs(part)]).sum(0)
     if norm:
-        out, new_res = comm.linear_allreduce(x, w, res, gam, 1e-5)
+        out, new_res = comm.linear_allreduce(x, w, res, gam, 1e-5, fused=None if M == 128 else True)
         torch.cuda.synchronize()
         comm.check()
         s = (total + res.float()).to(dtype).float()
