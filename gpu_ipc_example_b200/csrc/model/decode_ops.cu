@@ -499,6 +499,7 @@ int decode_attention_splits(int batch, int hkv, int ctx, int sm_count) {
   int s = (2 * sm_count) / (batch * hkv);
   if (s >= 8 && s < 12) s = 8;
   else if (s >= 4 && s < 6) s = 4;
+  if (const char* e = std::getenv("B200IPC_ATTN_SPLITS")) s = std::atoi(e);  // experiments
   const int by_len = (ctx + 63) / 64;
   if (s > by_len) s = by_len;
   if (s < 1) s = 1;
