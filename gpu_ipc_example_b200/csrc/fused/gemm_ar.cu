@@ -172,7 +172,7 @@ static CollInfo fused_gemm_decode(Comm& comm, DType t, const GemmArPtrs* ptrs, i
   args.local_only = local_only ? 1 : 0;
   // few rows, many CTAs: several CTAs share a row in the exchange, so that its transactions leave from many SMs
   int parts = 1;
-  if (with_norm && W > 1 && !local_only && std::getenv("B200IPC_GEMM_ROW_PARTS_OFF") == nullptr)
+  if (with_norm && !local_only && std::getenv("B200IPC_GEMM_ROW_PARTS_OFF") == nullptr)  // also without an exchange: 4x the CTAs per row
     while (parts < 8 && M * parts * 2 <= ctas && (N / 2) % (parts * 2 * 4) == 0) parts *= 2;
   args.row_parts = parts;
   args.landing_off = landing_off;

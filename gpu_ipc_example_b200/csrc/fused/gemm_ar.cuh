@@ -262,12 +262,24 @@ struct RowCtx {
   int m_tiles, n_tiles;
   int* fail;  // shared-memory flag of the thread group
 
+  // LOCAL: the flag is raised by a CTA of this GPU (device-scope release): relaxed polls and ONE device-scope
+  // fence once the value is there, instead of a system-scope acquire on every poll.
+  template <bool LOCAL = false>
   __device__ bool poll_flag(const uint32_t* fp, int src, int nt, int site) const {
     uint32_t* abort_word = reinterpret_cast<uint32_t*>(me->heap + lay->ctrl_off + kCtrlAbortOff);
     uint32_t spins = 0;
     uint64_t t0 = 0;
     for (;;) {
-      const uint32_t seen = ld_acquire_sys_u32(fp);
+      uint32_t seen;
+      if constexpr (LOCAL) {
+        seen = ld_volatile_u32(fp);
+        if (seen == epoch) {
+          asm volatile("fence.acq_rel.gpu;" ::: "memory");
+          return true;
+        }
+      } else {
+        seen = ld_acquire_sys_u32(fp);
+      }
       if (seen == epoch) return true;
       if ((++spins & 0x3fu) == 0) {
         if (ld_volatile_u32(abort_word) != 0 || *reinterpret_cast<volatile int*>(fail)) {
@@ -319,7 +331,7 @@ struct RowCtx {
   __device__ bool wait_local_tiles(int tid, int nthr) const {
     const uint32_t* base = reinterpret_cast<const uint32_t*>(me->heap + args->flags_off);
     bool ok = true;
-    for (int f = tid; f < n_tiles && ok; f += nthr) ok = poll_flag(base + f, me->rank, f, 23);
+    for (int f = tid; f < n_tiles && ok; f += nthr) ok = poll_flag<true>(base + f, me->rank, f, 23);
     return ok;
   }
 
