@@ -428,6 +428,19 @@ class Communicator:
     def seq(self) -> int:
         return self._C.seq(self._h)
 
+    def state_dict(self) -> dict:
+        """What a job has to carry over a checkpoint: the flag sequence number (rings of a fresh communicator are
+        zero, so any later sequence number is safe), the algorithm cut-offs and the safe-format switch.  The
+        reference keeps the same single piece of state in its `-f` flag (main.cpp:185 there)."""
+        return {"seq": int(self.seq), "world": int(self.world), "safe_protocols": bool(self.safe_protocols)}
+
+    def load_state_dict(self, state: dict) -> None:
+        if int(state.get("world", self.world)) != self.world:
+            raise ValueError(f"checkpoint is from a world of {state['world']}, this communicator has {self.world} ranks")
+        self.set_seq(int(state["seq"]))
+        if state.get("safe_protocols"):
+            self._C.set_safe_protos(self._h, True)
+
     # ------------------------------------------------------------------ protocol safety
     def soak(self, algos=("simple_pcie_p", "simple", "small_pcie_p", "small"), min_transactions: int = 100000,
              nelems: int = 1 << 20) -> dict:

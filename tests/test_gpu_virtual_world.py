@@ -225,6 +225,25 @@ def test_sequence_wrap_resets_the_rings(comm):
     assert comm.seq < 0x80000000
 
 
+def test_checkpoint_and_resume_of_the_only_state():
+    """A communicator's state is its flag sequence number: a new communicator that starts from the saved one
+    keeps producing flags no old ring entry can match."""
+    with Communicator.virtual(4, 0, staging_bytes=16 << 20) as a:
+        for n in (4096, 70000):
+            _check_allreduce(a, "simple", n, torch.float16)
+        state = a.state_dict()
+        assert state["seq"] > 0 and state["world"] == 4
+    with Communicator.virtual(4, 0, staging_bytes=16 << 20) as b:
+        b.load_state_dict(state)
+        assert b.seq == state["seq"]
+        for n in (4096, 70000):
+            _check_allreduce(b, "simple_pcie_p", n, torch.float16)
+        assert b.seq > state["seq"]
+    with Communicator.virtual(2, 0, staging_bytes=16 << 20) as c:
+        with pytest.raises(ValueError):
+            c.load_state_dict(state)
+
+
 def test_auto_picks_by_size(comm):
     # the built-in table (measured on NVLink) must at least be correct at every size class
     for n in (1024, 70000, 300000, 1 << 20, 3 << 20):
