@@ -57,7 +57,7 @@ def parse_json_rows(text: str, world: int, collective: str = "all_reduce", place
         r = json.loads(line)
         if r["world"] != world or r["collective"] != collective or r["placement"] != placement:
             continue
-        if r["algo"] in ("auto", "allgather_auto") or r.get("timing") == "graph_replay":
+        if r["algo"] in ("auto", "allgather_auto", "reduce_scatter") or r.get("timing") == "graph_replay":
             continue
         if symmetric is not None and bool(r.get("symmetric")) != symmetric and r["algo"] in ("bulk", "nvls"):
             continue
@@ -162,8 +162,25 @@ def main():
     ap.add_argument("--from-json", default=None, help="file of rows written by `bin/main --json`")
     ap.add_argument("--symmetric", action="store_true", help="large-message kernels on buffers inside the symmetric heap")
     ap.add_argument("--max-rows", type=int, default=0, help="best table with at most this many rows (0: every winner)")
+    ap.add_argument("--collective", default="all_reduce", choices=["all_reduce", "all_gather", "reduce_scatter"],
+                    help="with --from-json: which collective's rows to read (all-gather and reduce-scatter print cut-offs "
+                         "by algorithm name; their `auto` rules live in Comm::all_gather / Comm::reduce_scatter)")
     args = ap.parse_args()
     tables: Dict[str, Dict[int, float]] = {}
+    if args.from_json and args.collective != "all_reduce":
+        with open(args.from_json) as f:
+            tables = parse_json_rows(f.read(), args.np, collective=args.collective, placement="out_of_place",
+                                     symmetric=args.symmetric)
+        nccl = {a: tables.pop(a) for a in [a for a in tables if a.startswith("nccl")]}
+        rows = best_per_size(tables)
+        print(f"# world {args.np}, {args.collective}: fastest algorithm per size (NCCL in brackets)")
+        for elems, algo, us in rows:
+            ref = [t[elems] for t in nccl.values() if elems in t]
+            print(f"#   {elems * 2:>12} B  {algo:<32} {us:8.1f} us" + (f"   ({ref[0]:.1f})" if ref else ""))
+        table = best_table(tables, args.max_rows, skip=()) if args.max_rows > 0 else merge_rows(rows)
+        for nbytes, algo in table:
+            print(f"up to {nbytes if nbytes else 'any size':>12} B: {algo}")
+        return
     if args.from_json:
         with open(args.from_json) as f:
             tables = parse_json_rows(f.read(), args.np, symmetric=args.symmetric)

@@ -94,3 +94,28 @@ def test_tuner_reads_json_rows_and_limits_the_row_count():
     assert [a for _, a in every] == ["oneshot:ll512", "parallel:ll512", "bisect:ll512", "nvls"]
     three = tune.best_table(tables, 3)
     assert three == [(2 << 12, "oneshot:ll512"), (2 << 16, "parallel:ll512"), (0, "nvls")]
+
+
+def test_tuner_cut_offs_for_all_gather_and_reduce_scatter(tmp_path, capsys, monkeypatch):
+    """`--collective`: the same rows give the cut-offs of the other two collectives (NCCL rows are shown, never picked)."""
+    import json
+    import sys
+
+    from gpu_ipc_example_b200 import tune
+
+    rows = []
+    times = {"allgather_direct": [5, 6, 30, 90], "allgather_bulk": [12, 12, 20, 70], "allgather_simple": [9, 9, 25, 50],
+             "nccl_allgather": [4, 4, 4, 4], "allgather_auto": [1, 1, 1, 1]}
+    for algo, ts in times.items():
+        for e, us in zip((10, 14, 18, 22), ts):
+            rows.append(json.dumps({"collective": "all_gather", "algo": algo, "world": 8, "placement": "out_of_place", "symmetric": False,
+                                    "elements": 1 << e, "us_median": us}))
+    path = tmp_path / "rows.jsonl"
+    path.write_text("\n".join(rows) + "\n")
+    monkeypatch.setattr(sys, "argv", ["tune", "--from-json", str(path), "--np", "8", "--collective", "all_gather", "--max-rows", "3"])
+    tune.main()
+    out = capsys.readouterr().out
+    assert "nccl" not in out.split("up to", 1)[1] and "allgather_auto" not in out
+    cut = [line.split(": ")[1] for line in out.splitlines() if line.startswith("up to")]
+    assert cut == ["allgather_direct", "allgather_bulk", "allgather_simple"]
+    assert "(4.0)" in out  # the NCCL time beside every winner
