@@ -301,19 +301,37 @@ def run(args, json_out, state):
             h.normal_(0, 1e-3)
         host_out = torch.empty(1024, dtype=torch.float16).pin_memory()
 
+        # The upload of step i + 1 runs on its own stream while step i is reduced (the buffers rotate, so the two
+        # never touch the same memory); every step still uploads its own input and reads its own result back.
+        copy_stream = torch.cuda.Stream()
+        uploaded = [torch.cuda.Event() for _ in range(nbuf)]
+        consumed = [torch.cuda.Event() for _ in range(nbuf)]
+        for ev in consumed:
+            ev.record()
+
+        def upload(i):
+            b = bufs[i % nbuf]
+            copy_stream.wait_event(consumed[i % nbuf])  # the all-reduce that last used this buffer is done
+            with torch.cuda.stream(copy_stream):
+                for t in (b if isinstance(b, list) else [b]):
+                    t.copy_(host_in[i % 2], non_blocking=True)
+                uploaded[i % nbuf].record(copy_stream)
+
         def e2e_step(i):
             b = bufs[i % nbuf]
             first = b[0] if isinstance(b, list) else b
-            if isinstance(b, list):
-                for t in b:
-                    t.copy_(host_in[i % 2], non_blocking=True)
-            else:
-                b.copy_(host_in[i % 2], non_blocking=True)
+            main = torch.cuda.current_stream()
+            if i == 0:
+                upload(0)
+            upload(i + 1)  # one step ahead (the last call uploads one buffer that nothing consumes)
+            main.wait_event(uploaded[i % nbuf])
             comm.all_reduce(b, None, args.algo)
             host_out.copy_(first[:1024], non_blocking=True)
+            consumed[i % nbuf].record(main)
 
         for i in range(3):
             e2e_step(i)
+        torch.cuda.synchronize()
         s2 = timed(e2e_step, steps)
         h2d = nbytes * (emu_world if not multi else 1)
         e2e = {"value": round(busbw(nbytes, s2 / steps, emu_world), 3), "unit": "GB/s", "ms_per_step": round(s2 / steps * 1e3, 5),
