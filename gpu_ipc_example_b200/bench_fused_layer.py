@@ -293,7 +293,7 @@ def main_ag(args):
         full = torch.empty(M, K, device="cuda", dtype=dtype)
 
         def fused(i):
-            return comm.allgather_linear(shard, weights[i % ncopy])
+            return comm.allgather_linear(shard, weights[i % ncopy], fused=True)
 
         def ours_two_step(i):
             comm.all_gather(shard, full)

@@ -158,7 +158,7 @@ def check_ag_linear(comm, M, K, N):
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).half()
     x = torch.cat(gather_inputs(shard))
     for _ in range(3):
-        out = comm.allgather_linear(shard, w)
+        out = comm.allgather_linear(shard, w, fused=(_ != 2))
         torch.cuda.synchronize()
         comm.check()
         torch.testing.assert_close(out.float(), x.float() @ w.float().t(), atol=3e-2, rtol=1e-2)

@@ -139,7 +139,7 @@ def test_allgather_linear(world):
             ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).half() for _ in range(world)]
             shards = list(x.chunk(world, dim=0))
             for rep in range(3):  # the gathered-input buffer alternates between two halves
-                outs = comm.allgather_linear([s.contiguous() for s in shards], ws)
+                outs = comm.allgather_linear([s.contiguous() for s in shards], ws, fused=True if rep < 2 else None)
                 torch.cuda.synchronize()
                 comm.check()
                 for o, w in zip(outs, ws):
