@@ -721,6 +721,7 @@ CollInfo Comm::reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, vo
     info.sched = SchedKind::Bulk;
     return info;
   }
+  const bool was_auto = algo.automatic;
   if (algo.automatic) {
     algo = AlgoSpec{};
     // small inputs: one flag-in-data push to each slice's owner, no barrier
@@ -733,8 +734,16 @@ CollInfo Comm::reduce_scatter(AlgoSpec algo, DType t, const void* const* ins, vo
       algo.sched = SchedKind::Bulk;
     }
   }
-  if (algo.sched == SchedKind::Parallel)
-    return launch_ll(LLOpId::RsParallel, algo, t, ins, outs, nelems, geom, stream, extra_flags);
+  if (algo.sched == SchedKind::Parallel) {
+    if (!was_auto) return launch_ll(LLOpId::RsParallel, algo, t, ins, outs, nelems, geom, stream, extra_flags);
+    // `auto`: a device on which fewer wires can be resident than the cut-off assumes takes the barrier kernel instead
+    // (the geometry check throws before anything is launched or any sequence number is taken)
+    try {
+      return launch_ll(LLOpId::RsParallel, algo, t, ins, outs, nelems, geom, stream, extra_flags);
+    } catch (const std::exception&) {
+      algo.sched = SchedKind::Bulk;
+    }
+  }
   B200_REQUIRE(algo.sched == SchedKind::Bulk || algo.sched == SchedKind::Nvls,
                "reduce-scatter runs on the parallel (flag-in-data), bulk or nvls schedules");
   return launch_bulk(BulkModeId::ReduceScatter, algo.sched == SchedKind::Nvls, t, ins, outs, nelems, geom, stream,
